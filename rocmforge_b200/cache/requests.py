@@ -13,9 +13,10 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None      # size of a value head where it differs from a key head's
 
     def group_key(self):
-        return ("kv", self.n_kv_heads, self.head_dim, self.window)
+        return ("kv", self.n_kv_heads, self.head_dim, self.window, self.v_head_dim)
 
 
 @dataclass(frozen=True)

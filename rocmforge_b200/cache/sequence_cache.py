@@ -40,9 +40,13 @@ class KVGroup:
         self.max_pages_per_seq = max_pages_per_seq
         self.window = request.window
         self.pool = FreeList(n_pages, "cache page")
-        # [owner, k|v, page, kv_head, position in page, head_dim]
-        self.storage = torch.zeros((len(self.owners), 2, n_pages, request.n_kv_heads, PAGE, request.head_dim),
-                                   dtype=dtype, device=device)
+        # [owner, k|v, page, kv_head, position in page, head_dim]; values of another head size than keys have a tensor
+        # of their own (storage then holds the keys alone)
+        self.separate_values = request.v_head_dim is not None and request.v_head_dim != request.head_dim
+        self.storage = torch.zeros((len(self.owners), 1 if self.separate_values else 2, n_pages, request.n_kv_heads, PAGE,
+                                    request.head_dim), dtype=dtype, device=device)
+        self.value_storage = (torch.zeros((len(self.owners), 1, n_pages, request.n_kv_heads, PAGE, request.v_head_dim),
+                                          dtype=dtype, device=device) if self.separate_values else None)
         self.table = np.full((max_slots, max_pages_per_seq), -1, dtype=np.int32)
         self.table_dev = torch.zeros((max_slots, max_pages_per_seq), dtype=torch.int32, device=device)
         self._dirty: Dict[int, List[int]] = {}          # slot -> [lo, hi) of changed entries
@@ -144,6 +148,8 @@ class KVGroup:
         return self.storage[self.index_of[owner], 0]
 
     def v_pages(self, owner: int) -> torch.Tensor:
+        if self.separate_values:
+            return self.value_storage[self.index_of[owner], 0]
         return self.storage[self.index_of[owner], 1]
 
 
@@ -195,8 +201,19 @@ class SequenceCache:
         by_key: Dict[tuple, List[int]] = {}
         self._kv_request: Dict[tuple, KVRequest] = {}
         self.states: Dict[int, StateView] = {}
+        # a mixer made of several (side by side) asks with a dict {name: request}: every entry is kept under the
+        # owner (owner, name), and the mixer's view is the dict of its entries' views
+        self._parts_of: Dict[int, List[str]] = {}
+        flat = {}
         for owner in sorted(requests):
             req = requests[owner]
+            if isinstance(req, dict):
+                self._parts_of[owner] = list(req)
+                for name, r in req.items():
+                    flat[(owner, name)] = r
+            else:
+                flat[owner] = req
+        for owner, req in flat.items():
             if req is None:
                 continue
             if isinstance(req, KVRequest):
@@ -317,7 +334,9 @@ class SequenceCache:
     def state_view(self, owner: int) -> StateView:
         return self.states[owner]
 
-    def view(self, owner: int, writes: bool = True):
+    def view(self, owner, writes: bool = True):
+        if owner in self._parts_of:
+            return {name: self.view((owner, name), writes) for name in self._parts_of[owner]}
         if owner in self._group_of:
             return self.kv_view(owner, writes)
         if owner in self.states:
@@ -336,5 +355,6 @@ class SequenceCache:
 
     def memory_bytes(self) -> int:
         n = sum(g.storage.numel() * g.storage.element_size() for g in self.groups)
+        n += sum(g.value_storage.numel() * g.value_storage.element_size() for g in self.groups if g.separate_values)
         n += sum(t.numel() * t.element_size() for v in self.states.values() for t in v.tensors.values())
         return n

@@ -40,6 +40,8 @@ def architecture_for(name: str) -> Architecture:
 
 def architecture_name(raw: dict) -> str:
     archs = raw.get("architectures")
+    if not archs and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]                    # designs that name themselves with one string
     if not archs:
         raise MissingKey("architectures")
     if not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):

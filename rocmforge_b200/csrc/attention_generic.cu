@@ -40,15 +40,16 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ seq_slot, const int* __restrict__ block_table,
-                         int max_pages, int nh, int nkv, int hd, float scale, int window, int hpb) {
+                         int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
+                         const float* __restrict__ slopes, int window, int hpb) {
     constexpr int ACC = ATT_GB * (CK == 128 ? 256 : ATT_MAX_HD) / ATT_THREADS;     // (head, dim) pairs of a thread at most
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
-    const int ldk = hd + 1;                         // a key row per thread: odd stride, no bank conflicts
+    const int ldk = hd + 1, ldv = hdv + 1;          // a key row per thread: odd stride, no bank conflicts
     float* qs = smem;                               // [GB][hd]
-    float* kv = qs + ATT_GB * hd;                   // [CK][hd + 1]: the chunk's keys, then its values
-    float* probs = kv + CK * ldk;                   // [GB][CK]
+    float* kv = qs + ATT_GB * hd;                   // [CK][max(hd, hdv) + 1]: the chunk's keys, then its values
+    float* probs = kv + CK * (max(hd, hdv) + 1);    // [GB][CK]
     float* red = probs + ATT_GB * CK;               // [ATT_WARPS][GB]
 
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -58,9 +59,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int* bt = block_table + (size_t)slot * max_pages;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
 
-    const bool vec = (hd & 3) == 0;                 // rows of whole 4-element groups: 16-byte (8-byte) loads
-    const int hq = hd >> 2;
-    auto load_chunk = [&](const T* __restrict__ pages, int c0, int cnt) {
+    // rows of whole 4-element groups: 16-byte (8-byte) loads
+    auto load_chunk = [&](const T* __restrict__ pages, int c0, int cnt, int hd, int ldk) {
+        const bool vec = (hd & 3) == 0;
+        const int hq = hd >> 2;
         if (vec) {
             // the chunk as cnt * hd/4 groups of four elements, eight independent loads per thread in flight
             const int total = cnt * hq;
@@ -110,7 +112,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         for (int c0 = lo; c0 <= pos; c0 += CK) {
             const int cnt = min(CK, pos - c0 + 1);
             __syncthreads();                        // the values of the chunk before are used up (and qs is written)
-            load_chunk(k_pages, c0, cnt);
+            load_chunk(k_pages, c0, cnt, hd, ldk);
             __syncthreads();
             // ---- scores of key tid against every head of the pass
             float s[ATT_GB];
@@ -129,7 +131,12 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 }
 #pragma unroll
                 for (int g = 0; g < ATT_GB; ++g)
-                    if (g < gb) s[g] = d[g] * scale;
+                    if (g < gb) {
+                        float sc = d[g] * scale;
+                        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);          // scores capped smoothly at +-softcap
+                        if (slopes != nullptr) sc -= slopes[kvh * G + g0 + g] * (float)(pos - (c0 + tid));   // a bias that grows with the distance
+                        s[g] = sc;
+                    }
             }
             // ---- the chunk's maximum per head: warps, then the block
 #pragma unroll
@@ -157,7 +164,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 const float w = warp_sum(p[g]);
                 if (lane == 0) red[warp * ATT_GB + g] = w;
             }
-            load_chunk(v_pages, c0, cnt);
+            load_chunk(v_pages, c0, cnt, hdv, ldv);
             __syncthreads();
 #pragma unroll
             for (int g = 0; g < ATT_GB; ++g) {
@@ -170,8 +177,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
             for (int i = 0; i < ACC; ++i) {
                 const int e = tid + i * ATT_THREADS;
-                if (e < gb * hd) {
-                    const int g = e / hd, d = e - g * hd;
+                if (e < gb * hdv) {
+                    const int g = e / hdv, d = e - g * hdv;
                     float c = 0.f;
 #pragma unroll
                     for (int gg = 0; gg < ATT_GB; ++gg) if (gg == g) c = corr[gg];
@@ -182,12 +189,12 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
                     int j = 0;
                     for (; j + 3 < cnt; j += 4) {
-                        a0 = fmaf(pr[j], vv[j * ldk], a0);
-                        a1 = fmaf(pr[j + 1], vv[(j + 1) * ldk], a1);
-                        a2 = fmaf(pr[j + 2], vv[(j + 2) * ldk], a2);
-                        a3 = fmaf(pr[j + 3], vv[(j + 3) * ldk], a3);
+                        a0 = fmaf(pr[j], vv[j * ldv], a0);
+                        a1 = fmaf(pr[j + 1], vv[(j + 1) * ldv], a1);
+                        a2 = fmaf(pr[j + 2], vv[(j + 2) * ldv], a2);
+                        a3 = fmaf(pr[j + 3], vv[(j + 3) * ldv], a3);
                     }
-                    for (; j < cnt; ++j) a0 = fmaf(pr[j], vv[j * ldk], a0);
+                    for (; j < cnt; ++j) a0 = fmaf(pr[j], vv[j * ldv], a0);
                     acc[i] = acc[i] * c + ((a0 + a1) + (a2 + a3));
                 }
             }
@@ -195,12 +202,12 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
         for (int i = 0; i < ACC; ++i) {
             const int e = tid + i * ATT_THREADS;
-            if (e < gb * hd) {
-                const int g = e / hd, d = e - g * hd;
+            if (e < gb * hdv) {
+                const int g = e / hdv, d = e - g * hdv;
                 float l = 0.f;
 #pragma unroll
                 for (int gg = 0; gg < ATT_GB; ++gg) if (gg == g) l = l_run[gg];
-                out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * hd + d] = Cvt<T>::from_f32(l > 0.f ? acc[i] / l : 0.f);
+                out[(size_t)t * out_stride + (size_t)(kvh * G + g0 + g) * hdv + d] = Cvt<T>::from_f32(l > 0.f ? acc[i] / l : 0.f);
             }
         }
     }
@@ -209,9 +216,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 template <typename T, int CK>
 static int launch_ck(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                      const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
-                     const int* block_table, int max_pages, int nh, int nkv, int hd, float scale, int window,
-                     int T_, cudaStream_t st) {
-    const size_t smem = ((size_t)ATT_GB * hd + (size_t)CK * (hd + 1) + ATT_GB * CK + ATT_WARPS * ATT_GB) * sizeof(float);
+                     const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
+                     const float* slopes, int window, int T_, cudaStream_t st) {
+    const int hm = hd > hdv ? hd : hdv;
+    const size_t smem = ((size_t)ATT_GB * hd + (size_t)CK * (hm + 1) + ATT_GB * CK + ATT_WARPS * ATT_GB) * sizeof(float);
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<T, CK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -231,7 +239,7 @@ static int launch_ck(const void* q, int q_stride, void* out, int out_stride, con
     rf_launch(attention_generic_kernel<T, CK>, grid, dim3(ATT_THREADS), smem, st,
         reinterpret_cast<const T*>(q), q_stride, reinterpret_cast<T*>(out), out_stride,
         reinterpret_cast<const T*>(k_pages), reinterpret_cast<const T*>(v_pages), tok_seq, tok_pos, seq_slot,
-        block_table, max_pages, nh, nkv, hd, scale, window, hpb);
+        block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, hpb);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -239,15 +247,15 @@ static int launch_ck(const void* q, int q_stride, void* out, int out_stride, con
 template <typename T>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                   const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
-                  const int* block_table, int max_pages, int nh, int nkv, int hd, float scale, int window,
-                  int T_, cudaStream_t st) {
+                  const int* block_table, int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
+                  const float* slopes, int window, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
-    if (hd <= 0 || hd > ATT_MAX_HD || nkv <= 0 || nh % nkv || nkv > 65535) return RF_ERR_UNSUPPORTED;
-    if (hd <= 256)
+    if (hd <= 0 || hd > ATT_MAX_HD || hdv <= 0 || hdv > ATT_MAX_HD || nkv <= 0 || nh % nkv || nkv > 65535) return RF_ERR_UNSUPPORTED;
+    if (hd <= 256 && hdv <= 256)
         return launch_ck<T, 128>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                                 max_pages, nh, nkv, hd, scale, window, T_, st);
+                                 max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
     return launch_ck<T, 64>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                            max_pages, nh, nkv, hd, scale, window, T_, st);
+                            max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
 }
 
 extern "C" int rf_attention_generic(int dtype, const void* q, int q_stride, void* out, int out_stride,
@@ -257,7 +265,22 @@ extern "C" int rf_attention_generic(int dtype, const void* q, int q_stride, void
                                     cudaStream_t st) {
     return dtype == 0
         ? launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
-                        max_pages, nh, nkv, hd, scale, window, T_, st)
+                        max_pages, nh, nkv, hd, hd, scale, 0.f, nullptr, window, T_, st)
         : launch<__nv_bfloat16>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
-                                block_table, max_pages, nh, nkv, hd, scale, window, T_, st);
+                                block_table, max_pages, nh, nkv, hd, hd, scale, 0.f, nullptr, window, T_, st);
+}
+
+// The same with the options of other designs: values of another head size (hdv; value pages are
+// [n_pages, nkv, RF_PAGE, hdv], the output [T, nh * hdv]), scores capped as softcap * tanh(score / softcap)
+// (softcap 0: not capped) and, after the cap, lowered by slopes[head] * (query position - key position) (slopes null: no bias).
+extern "C" int rf_attention_generic_ext(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                                        const void* k_pages, const void* v_pages, const int* tok_seq,
+                                        const int* tok_pos, const int* seq_slot, const int* block_table,
+                                        int max_pages, int nh, int nkv, int hd, int hdv, float scale, float softcap,
+                                        const float* slopes, int window, int T_, cudaStream_t st) {
+    return dtype == 0
+        ? launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table,
+                        max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st)
+        : launch<__nv_bfloat16>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
+                                block_table, max_pages, nh, nkv, hd, hdv, scale, softcap, slopes, window, T_, st);
 }

@@ -462,6 +462,141 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ a, size_
     }
 }
 
+// ---------------------------------------------------------------- squared ReLU
+// a = max(x, 0)^2, evaluated in 32-bit.
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ a, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(Cvt<T>::to_f32(x[idx]), 0.f);
+        a[idx] = Cvt<T>::from_f32(v * v);
+    }
+}
+
+// ---------------------------------------------------------------- a row vector added to every row of the stream
+template <typename T>
+__global__ void add_row_kernel(float* __restrict__ h, const T* __restrict__ vec, size_t n, int H) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
+        h[idx] += Cvt<T>::to_f32(vec[idx % H]);
+}
+
+// ---------------------------------------------------------------- a normed branch added into the stream
+// The residual update of a block that norms its sub-layers' outputs as well as their inputs, all in 32-bit:
+//   m = a0                                            (one branch), or
+//   m = (rms(a0) * w0 + rms(a1) * w1) / 2             (two branches side by side, each normed with its own weight)
+//   h += rms(m) * w_post (+ extra)                    (extra: a row vector that the schedule adds before the next layer)
+//   y_next = rms(h) * w_next in the compute dtype     (the norm that reads the stream next, if the caller knows it)
+// with rms(x) = x / sqrt(mean(x^2) + eps).  A block per row; the row stays in shared memory between the passes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, const void* __restrict__ w0,
+                       const float* __restrict__ a1, const void* __restrict__ w1, const void* __restrict__ w_post,
+                       const void* __restrict__ extra, const void* __restrict__ w_next, T* __restrict__ y_next,
+                       int w_is_f32, float eps, int H) {
+    extern __shared__ float row[];                  // [H] + 34 for the sums
+    float* red = row + H;
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * H;
+    const float invH = 1.f / (float)H;
+    pdl_wait();
+    if (a1 != nullptr) {
+        float s0 = 0.f, s1 = 0.f;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float x = a0[base + c], z = a1[base + c];
+            s0 += x * x; s1 += z * z;
+        }
+        const float r0 = rsqrtf(block_sum(s0, red) * invH + eps);
+        const float r1 = rsqrtf(block_sum(s1, red) * invH + eps);
+        for (int c = threadIdx.x; c < H; c += blockDim.x)
+            row[c] = 0.5f * (a0[base + c] * r0 * load_vec(w0, w_is_f32, c) + a1[base + c] * r1 * load_vec(w1, w_is_f32, c));
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) row[c] = a0[base + c];
+    }
+    float sm = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) sm += row[c] * row[c];      // a thread reads what it wrote
+    const float rm = rsqrtf(block_sum(sm, red) * invH + eps);
+    float sh = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = h[base + c] + row[c] * rm * load_vec(w_post, w_is_f32, c);
+        if (extra != nullptr) v += load_vec(extra, w_is_f32, c);
+        h[base + c] = v;
+        row[c] = v;
+        sh += v * v;
+    }
+    if (y_next == nullptr) return;
+    const float rh = rsqrtf(block_sum(sh, red) * invH + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        y_next[base + c] = Cvt<T>::from_f32(row[c] * rh * load_vec(w_next, w_is_f32, c));
+}
+
+// ---------------------------------------------------------------- per-head unit norm + rotation + cache write
+// A warp per head of a token's q | k | v row: q heads and k heads have hd elements, v heads hdv.  The row comes in
+// the compute dtype or as n_partials 32-bit partial sums.  With unit_norm every q and k head is divided by its root
+// mean square (x / sqrt(mean(x^2) + eps), no weight, 32-bit); then the first rot_dim elements turn as in the kernel
+// above (rot_dim 0: none); q goes to q_out, k and v into the page of (slot, position).  Key pages are
+// [n_pages, nkv, RF_PAGE, hd], value pages [n_pages, nkv, RF_PAGE, hdv].
+template <typename T, bool PARTIALS>
+__global__ void __launch_bounds__(128)
+head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_partials, size_t partial_stride,
+                          T* __restrict__ q_out, int q_out_stride, int nh, int nkv, int hd, int hdv,
+                          const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
+                          const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+                          const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
+                          T* __restrict__ v_pages, int write_kv, int rot_dim, int interleaved, int unit_norm, float eps) {
+    extern __shared__ float heads_buf[];            // [warps][max(hd, hdv)]
+    pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int hmax = hd > hdv ? hd : hdv;
+    float* buf = heads_buf + warp * hmax;
+    const int pos = tok_pos[t];
+    const int slot = seq_slot[tok_seq[t]];
+    const int page = write_kv ? block_table[(size_t)slot * max_pages + pos / RF_PAGE] : 0;
+    const int rh = rot_dim >> 1;
+    pdl_wait();
+    const int n_heads_all = write_kv ? nh + 2 * nkv : nh;
+    for (int head = warp; head < n_heads_all; head += nwarp) {
+        const bool is_v = head >= nh + nkv;
+        const int n = is_v ? hdv : hd;
+        const int col = is_v ? (nh + nkv) * hd + (head - nh - nkv) * hdv : head * hd;
+        float ss = 0.f;
+        for (int e = lane; e < n; e += 32) {
+            float x;
+            if (PARTIALS) {
+                const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride + col + e;
+                x = 0.f;
+                for (int sp = 0; sp < n_partials; ++sp) x += p[(size_t)sp * partial_stride];
+            } else {
+                x = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col + e]);
+            }
+            buf[e] = x;
+            ss += x * x;
+        }
+        float r = 1.f;
+        if (unit_norm && !is_v) r = rsqrtf(warp_sum(ss) / (float)n + eps);
+        __syncwarp();
+        T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
+               : !is_v ? k_pages + ((size_t)page * nkv + (head - nh)) * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd
+                       : v_pages + ((size_t)page * nkv + (head - nh - nkv)) * RF_PAGE * hdv + (size_t)(pos % RF_PAGE) * hdv;
+        for (int e = lane; e < n; e += 32) {
+            float x = buf[e] * r;
+            if (!is_v && e < rot_dim) {
+                int i, partner; bool first;
+                if (interleaved) { i = e >> 1; first = !(e & 1); partner = first ? e + 1 : e - 1; }
+                else { first = e < rh; i = first ? e : e - rh; partner = first ? e + rh : e - rh; }
+                float s, c;
+                sincosf((float)pos * inv_freq[i], &s, &c);
+                const float y = buf[partner] * r;
+                x = first ? x * c - y * s : x * c + y * s;
+            }
+            dst[e] = Cvt<T>::from_f32(x);
+        }
+        __syncwarp();
+    }
+}
+
 // ---------------------------------------------------------------- launchers
 template <typename T>
 static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
@@ -575,6 +710,67 @@ static int launch_swiglu(const void* gu, void* a, int T_, int I, cudaStream_t st
     return 0;
 }
 
+
+template <typename T>
+static int launch_relu2(const void* x, void* a, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    rf_launch(relu2_kernel<T>, dim3(blocks), dim3(256), 0, st, reinterpret_cast<const T*>(x), reinterpret_cast<T*>(a), (size_t)n);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_add_row(float* h, const void* vec, int T_, int H, cudaStream_t st) {
+    const size_t n = (size_t)T_ * H;
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    rf_launch(add_row_kernel<T>, dim3(blocks), dim3(256), 0, st, h, reinterpret_cast<const T*>(vec), n, H);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_branch_norm_add(float* h, const float* a0, const void* w0, const float* a1, const void* w1,
+                                  const void* w_post, const void* extra, const void* w_next, void* y_next,
+                                  int w_is_f32, float eps, int rows, int H, cudaStream_t st) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)(H + 34) * sizeof(float);
+    if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(branch_norm_add_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    rf_launch(branch_norm_add_kernel<T>, dim3(rows), dim3(256), smem, st, h, a0, w0, a1, w1, w_post, extra, w_next,
+              reinterpret_cast<T*>(y_next), w_is_f32, eps, H);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_head_norm_kv_write(const void* src, int row_stride, int n_partials, size_t partial_stride, void* q_out,
+                                     int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq,
+                                     const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
+                                     int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, int rot_dim,
+                                     int interleaved, int unit_norm, float eps, cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0) return RF_ERR_BAD_ARG;
+    const size_t smem = (size_t)4 * (hd > hdv ? hd : hdv) * sizeof(float);
+    if (smem > 48 * 1024) return RF_ERR_UNSUPPORTED;
+    if (n_partials > 0)
+        rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
+                  reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
+    else
+        rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
+                  reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 // dtype: 0 = float32, 1 = bfloat16
 extern "C" {
 int rf_embed(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
@@ -604,5 +800,33 @@ int rf_rope_kv_write(int dtype, const void* src, int row_stride, int n_partials,
 }
 int rf_swiglu(int dtype, const void* gu, void* a, int T_, int I, cudaStream_t st) {
     return dtype == 0 ? launch_swiglu<float>(gu, a, T_, I, st) : launch_swiglu<__nv_bfloat16>(gu, a, T_, I, st);
+}
+int rf_relu2(int dtype, const void* x, void* a, long long n, cudaStream_t st) {
+    return dtype == 0 ? launch_relu2<float>(x, a, n, st) : launch_relu2<__nv_bfloat16>(x, a, n, st);
+}
+int rf_add_row(int dtype, float* h, const void* vec, int T_, int H, cudaStream_t st) {
+    return dtype == 0 ? launch_add_row<float>(h, vec, T_, H, st) : launch_add_row<__nv_bfloat16>(h, vec, T_, H, st);
+}
+// a1 / w1 null: one branch, taken as it is; extra, w_next / y_next null: left out.  All weight vectors share w_is_f32.
+int rf_branch_norm_add(int dtype, float* h, const float* a0, const void* w0, const float* a1, const void* w1,
+                       const void* w_post, const void* extra, const void* w_next, void* y_next, int w_is_f32, float eps,
+                       int rows, int H, cudaStream_t st) {
+    return dtype == 0
+        ? launch_branch_norm_add<float>(h, a0, w0, a1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st)
+        : launch_branch_norm_add<__nv_bfloat16>(h, a0, w0, a1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st);
+}
+int rf_head_norm_kv_write(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride, void* q_out,
+                          int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq, const int* tok_seq,
+                          const int* tok_pos, const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
+                          void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, int unit_norm, float eps,
+                          cudaStream_t st) {
+    return dtype == 0
+        ? launch_head_norm_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride, nh, nkv,
+                                           hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, max_pages, k_pages,
+                                           v_pages, write_kv, T_, rot_dim, interleaved, unit_norm, eps, st)
+        : launch_head_norm_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride,
+                                                   nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                                                   max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
+                                                   unit_norm, eps, st);
 }
 }

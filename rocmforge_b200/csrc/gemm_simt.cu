@@ -48,11 +48,17 @@ __device__ __forceinline__ float4 load_k4(const T* __restrict__ base, int row, i
 
 // mode 0: Y (compute dtype) = acc + bias;  1: Y (float) = acc + bias;  2: Y (float) += acc + bias;
 // 3: Y (float) [split, M, N] = acc (partial sums of this split's K range; the bias is the consumer's)
-template <typename T, int BM>
+//
+// GROUPED: one launch for many weight matrices (the experts of a routed feed-forward).  tiles[0] is the number of row
+// tiles, then (group, first row, end row) per tile; rows are in the order the router's sort left them; a tile's rows
+// all use W + group * w_stride.  With row_map, row r of X is read from row_map[r] / row_div (a gather: the same
+// token's activations serve each of its choices).  Blocks beyond the tile count return at once.
+template <typename T, int BM, bool GROUPED = false>
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const void* __restrict__ bias,
                  int bias_is_f32, void* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int mode,
-                 int k_per_split, int vec_x, int vec_w) {
+                 int k_per_split, int vec_x, int vec_w, const int* __restrict__ tiles = nullptr,
+                 const int* __restrict__ row_map = nullptr, int row_div = 1, long long w_stride = 0) {
     constexpr int TM = BM / 16;                                  // token rows of a thread
     constexpr int XV = (BM * GS_BK / 4 + GS_THREADS - 1) / GS_THREADS;     // 16-byte loads of X per thread and block
     constexpr int WV = GS_BN * GS_BK / 4 / GS_THREADS;                      // ... of W (2)
@@ -61,7 +67,22 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const void* _
     __shared__ __align__(16) float Ws[2][GS_BK][LDW];
     pdl_trigger();
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * GS_BN;
+    int m0 = blockIdx.y * BM;
+    const int n0 = blockIdx.x * GS_BN;
+    __shared__ int src_row[GROUPED ? BM : 1];
+    if constexpr (GROUPED) {
+        pdl_wait();                                   // the tile table and the row map are the sort kernel's
+        if ((int)blockIdx.y >= tiles[0]) return;
+        const int* tl = tiles + 1 + 3 * blockIdx.y;
+        W += (size_t)tl[0] * w_stride;
+        m0 = tl[1];
+        M = tl[2];
+        if (threadIdx.x < BM) {
+            const int r = m0 + threadIdx.x;
+            src_row[threadIdx.x] = r < M ? (row_map != nullptr ? row_map[r] / row_div : r) : 0;
+        }
+        __syncthreads();
+    }
     const int k_begin = blockIdx.z * k_per_split;
     const int k_end = min(K, k_begin + k_per_split);
     const int lr = tid >> 2, lk = (tid & 3) * 4;                 // this thread's row and k offset inside a block load
@@ -74,8 +95,12 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const void* _
     auto fetch_x = [&](int k0) {
 #pragma unroll
         for (int i = 0; i < XV; ++i)
-            xr[i] = (lr + 64 * i < BM) ? load_k4(X, m0 + lr + 64 * i, M, ldx, k0 + lk, k_end, vec_x)
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr (GROUPED)
+                xr[i] = (lr + 64 * i < BM && m0 + lr + 64 * i < M)
+                    ? load_k4(X, src_row[lr + 64 * i], 0x7fffffff, ldx, k0 + lk, k_end, vec_x) : make_float4(0.f, 0.f, 0.f, 0.f);
+            else
+                xr[i] = (lr + 64 * i < BM) ? load_k4(X, m0 + lr + 64 * i, M, ldx, k0 + lk, k_end, vec_x)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
     };
     auto stash = [&](int buf) {                                  // registers -> shared memory, transposed to k-major
 #pragma unroll
@@ -172,8 +197,9 @@ static int launch_bm(const void* X, const void* W, const void* bias, int bias_is
     const size_t es = sizeof(T);
     const int vec_x = (reinterpret_cast<uintptr_t>(X) % (4 * es) == 0) && (ldx % 4 == 0);
     const int vec_w = (reinterpret_cast<uintptr_t>(W) % (4 * es) == 0) && (K % 4 == 0);
-    rf_launch(gemm_simt_kernel<T, BM>, grid, dim3(GS_THREADS), 0, st, reinterpret_cast<const T*>(X),
-              reinterpret_cast<const T*>(W), bias, bias_is_f32, Y, M, N, K, ldx, ldy, mode, per, vec_x, vec_w);
+    rf_launch(gemm_simt_kernel<T, BM, false>, grid, dim3(GS_THREADS), 0, st, reinterpret_cast<const T*>(X),
+              reinterpret_cast<const T*>(W), bias, bias_is_f32, Y, M, N, K, ldx, ldy, mode, per, vec_x, vec_w,
+              (const int*)nullptr, (const int*)nullptr, 1, 0LL);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -188,6 +214,36 @@ static int launch(const void* X, const void* W, const void* bias, int bias_is_f3
     if (M <= 32) return launch_bm<T, 32>(X, W, bias, bias_is_f32, Y, M, N, K, ldx, ldy, mode, splits, st);
     if (M <= 64) return launch_bm<T, 64>(X, W, bias, bias_is_f32, Y, M, N, K, ldx, ldy, mode, splits, st);
     return launch_bm<T, 128>(X, W, bias, bias_is_f32, Y, M, N, K, ldx, ldy, mode, splits, st);
+}
+
+template <typename T, int BM>
+static int launch_grouped_bm(const void* X, const void* W, void* Y, int max_tiles, int N, int K, int ldx, int ldy, int mode,
+                             const int* tiles, const int* row_map, int row_div, long long w_stride, cudaStream_t st) {
+    dim3 grid((N + GS_BN - 1) / GS_BN, max_tiles, 1);
+    if (grid.y > 65535) return RF_ERR_UNSUPPORTED;
+    const int per = (K + GS_BK - 1) / GS_BK * GS_BK;
+    const size_t es = sizeof(T);
+    const int vec_x = (reinterpret_cast<uintptr_t>(X) % (4 * es) == 0) && (ldx % 4 == 0);
+    const int vec_w = (reinterpret_cast<uintptr_t>(W) % (4 * es) == 0) && (K % 4 == 0) && (w_stride % 4 == 0);
+    rf_launch(gemm_simt_kernel<T, BM, true>, grid, dim3(GS_THREADS), 0, st, reinterpret_cast<const T*>(X),
+              reinterpret_cast<const T*>(W), (const void*)nullptr, 0, Y, 0, N, K, ldx, ldy, mode, per, vec_x, vec_w, tiles,
+              row_map, row_div, w_stride);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+// Y[r] = X[row_map[r] / row_div] * W[group of r]^T for the sorted rows r that `tiles` lists (BM rows a tile at most:
+// 16 or 64, the size the table was built for); mode 0: compute dtype, 1: float.
+extern "C" int rf_gemm_simt_grouped(int dtype, const void* X, const void* W, void* Y, int max_tiles, int BM, int N, int K,
+                                    int ldx, int ldy, int mode, const int* tiles, const int* row_map, int row_div,
+                                    long long w_stride, cudaStream_t st) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if (K <= 0 || (mode != 0 && mode != 1) || row_div < 1 || (BM != 16 && BM != 64)) return RF_ERR_BAD_ARG;
+    if (dtype == 0)
+        return BM == 16 ? launch_grouped_bm<float, 16>(X, W, Y, max_tiles, N, K, ldx, ldy, mode, tiles, row_map, row_div, w_stride, st)
+                        : launch_grouped_bm<float, 64>(X, W, Y, max_tiles, N, K, ldx, ldy, mode, tiles, row_map, row_div, w_stride, st);
+    return BM == 16 ? launch_grouped_bm<__nv_bfloat16, 16>(X, W, Y, max_tiles, N, K, ldx, ldy, mode, tiles, row_map, row_div, w_stride, st)
+                    : launch_grouped_bm<__nv_bfloat16, 64>(X, W, Y, max_tiles, N, K, ldx, ldy, mode, tiles, row_map, row_div, w_stride, st);
 }
 
 extern "C" int rf_gemm_simt(int dtype, const void* X, const void* W, const void* bias, int bias_is_f32,

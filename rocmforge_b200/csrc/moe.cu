@@ -1,0 +1,117 @@
+// Routing of a mixture of experts: which experts a token uses, with what weights, and the tokens sorted by expert
+// so that one grouped product serves all experts of a step without the host ever learning the counts.
+//
+//   moe_route     per token: the `top` largest of E router logits (32-bit; of equal logits the lower index), and
+//                 the softmax over the chosen logits only
+//   moe_sort      counting sort of the T*top (token, choice) pairs by expert: perm[sorted row] = pair,
+//                 inv[pair] = sorted row, and the table of row tiles for the grouped product
+//                 (tiles[0] = number of tiles, then (expert, first row, end row) per tile; a tile never spans experts)
+//   moe_combine   out[t] = sum over the token's choices, in the order of the choices, of weight * expert output row
+// A row of the grouped product depends on its own token alone, so where the sort puts a pair changes no bit.
+#include "common.cuh"
+
+#define MOE_MAX_TOP 16
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ idx,
+                                 float* __restrict__ w, int T_) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T_) return;
+    const float* z = logits + (size_t)t * E;
+    int chosen[MOE_MAX_TOP];
+    float val[MOE_MAX_TOP];
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bv = -INFINITY;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int c = 0; c < k; ++c) taken |= chosen[c] == e;
+            const float v = z[e];
+            if (!taken && (best < 0 || v > bv)) { best = e; bv = v; }
+        }
+        chosen[k] = best;
+        val[k] = bv;
+    }
+    float sum = 0.f;
+    const float largest = val[0];
+    for (int k = 0; k < top; ++k) { val[k] = expf(val[k] - largest); sum += val[k]; }
+    for (int k = 0; k < top; ++k) {
+        idx[(size_t)t * top + k] = chosen[k];
+        w[(size_t)t * top + k] = val[k] / sum;
+    }
+}
+
+// One block.  counts/cursors live in shared memory (E <= 1024).
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ idx, int n, int E, int BM, int* __restrict__ perm, int* __restrict__ inv,
+                int* __restrict__ offsets, int* __restrict__ tiles, int max_tiles) {
+    __shared__ int counts[1024];
+    __shared__ int cursor[1024];
+    pdl_trigger();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&counts[idx[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = off;
+            cursor[e] = off;
+            for (int r = off; r < off + counts[e] && nt < max_tiles; r += BM) {
+                tiles[1 + 3 * nt] = e;
+                tiles[2 + 3 * nt] = r;
+                tiles[3 + 3 * nt] = min(r + BM, off + counts[e]);
+                ++nt;
+            }
+            off += counts[e];
+        }
+        offsets[E] = off;
+        tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int r = atomicAdd(&cursor[idx[i]], 1);
+        perm[r] = i;
+        inv[i] = r;
+    }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ inv, const float* __restrict__ w,
+                                   float* __restrict__ out, int top, int H, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / H, c = i - t * H;
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(w[t * top + k], y[(size_t)inv[t * top + k] * H + c], acc);
+        out[i] = acc;
+    }
+}
+
+extern "C" {
+int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_, cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (top < 1 || top > MOE_MAX_TOP || top > E) return RF_ERR_UNSUPPORTED;
+    rf_launch(moe_route_kernel, dim3((T_ + 127) / 128), dim3(128), 0, st, logits, E, top, idx, w, T_);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+int rf_moe_sort(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
+                cudaStream_t st) {
+    if (n <= 0) return 0;
+    if (E < 1 || E > 1024 || BM < 1) return RF_ERR_UNSUPPORTED;
+    rf_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, st, idx, n, E, BM, perm, inv, offsets, tiles, max_tiles);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+int rf_moe_combine(const float* y, const int* inv, const float* w, float* out, int top, int H, int T_, cudaStream_t st) {
+    const size_t n = (size_t)T_ * H;
+    if (n == 0) return 0;
+    const size_t blocks = (n + 255) / 256;
+    rf_launch(moe_combine_kernel, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st, y, inv, w, out, top, H, n);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+}

@@ -30,6 +30,7 @@ class ScheduleEntry:
     this execution reads instead of keeping its own (it then writes nothing)."""
     layer: int
     kv_from: Optional[int] = None
+    pass_index: Optional[int] = None     # row of ModelSpec.pass_offsets that is added to the stream right before this execution
 
 
 @dataclass
@@ -48,10 +49,14 @@ class ModelSpec:
     hidden_size: int
     max_position: int
     stop_token_ids: List[int] = field(default_factory=list)
+    pass_offsets: Optional[Part] = None              # parts.offsets.PassOffsets, for schedules with pass_index
+    pass_offsets_prefix: str = ""
 
     def named_parts(self) -> Dict[str, Part]:
         """{tensor-name prefix: leaf part}."""
         out: Dict[str, Part] = {self.embedding_prefix: self.embedding}
+        if self.pass_offsets is not None:
+            out[self.pass_offsets_prefix] = self.pass_offsets
         for prefix, block in zip(self.block_prefixes, self.blocks):
             for sub, part in block.sub_parts().items():
                 out[prefix + sub] = part
@@ -72,6 +77,8 @@ class ModelSpec:
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}; there are {len(self.blocks)}")
+            if e.pass_index is not None and self.pass_offsets is None:
+                raise ValueError(f"schedule entry {i} names pass {e.pass_index}, but the model has no pass offsets")
             if e.kv_from is not None:
                 if not 0 <= e.kv_from < i or self.schedule[e.kv_from].kv_from is not None:
                     raise ValueError(f"schedule entry {i}: kv_from must name an earlier entry that owns a cache")
@@ -185,6 +192,8 @@ class Model:
         """The layers in schedule order on the batch that ``ctx`` describes."""
         spec = self.spec
         stream = ResidualStream(spec.embedding.forward(ctx, ctx.tokens))
+        if spec.schedule and spec.schedule[0].pass_index is not None:
+            spec.pass_offsets.add(ctx, stream, spec.schedule[0].pass_index)
         for i, entry in enumerate(spec.schedule):
             owner = i if entry.kv_from is None else entry.kv_from
             view = cache.view(owner, writes=entry.kv_from is None)
@@ -192,7 +201,13 @@ class Model:
             # rows and runs as a kernel of its own)
             nxt = spec.schedule[i + 1] if i + 1 < len(spec.schedule) else None
             stream.after_block = spec.blocks[nxt.layer].entry_norm() if nxt is not None else None
+            # the vector that the schedule adds before the next execution: a block may add it with its last update
+            stream.after_extra = (spec.pass_offsets.row(nxt.pass_index)
+                                  if nxt is not None and nxt.pass_index is not None else None)
             spec.blocks[entry.layer].forward(ctx, stream, view)
+            if stream.after_extra is not None:       # the block left it to us
+                spec.pass_offsets.add(ctx, stream, nxt.pass_index)
+                stream.after_extra = None
         stream.next_norm = stream.after_block = None
         if ctx.R == 0:
             return None

@@ -49,6 +49,8 @@ class ResidualStream:
         self.pending: Optional[torch.Tensor] = None
         self.next_norm = None
         self.after_block = None          # set by the model: the norm that reads the stream after this block
+        self.after_extra = None          # set by the model: a row vector [H] that the schedule adds to every row after this
+                                         # block; a block that fuses the addition into its last update sets this to None
         self.prepared = None
 
     def add_pending(self, t: torch.Tensor) -> None:

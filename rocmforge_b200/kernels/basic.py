@@ -196,16 +196,34 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
 
 def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                       tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
-                      out: torch.Tensor | None = None) -> torch.Tensor:
-    """Attention of the T new tokens over the paged cache (their own keys included)."""
-    need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table)
+                      out: torch.Tensor | None = None, *, v_head_dim: int | None = None, softcap: float | None = None,
+                      slopes: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of the T new tokens over the paged cache (their own keys included).
+
+    ``v_head_dim``: size of a value head where it differs from a key head's (the output is [T, heads * v_head_dim]);
+    ``softcap``: scores become softcap * tanh(score / softcap); ``slopes`` (float32 [heads]): after the cap, a score is
+    lowered by slopes[head] * (query position - key position)."""
+    need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table, slopes)
     T = q.shape[0]
+    vd = head_dim if v_head_dim is None else int(v_head_dim)
     need(q.dim() == 2 and q.stride(1) == 1, "attention: q must be [T, >= heads*head_dim] with unit inner stride")
     need(k_pages.dtype == q.dtype and v_pages.dtype == q.dtype, "attention: cache dtype differs from q")
     need(tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous()
-         and v_pages.shape == k_pages.shape and v_pages.is_contiguous(), "attention: bad cache page shape")
+         and tuple(v_pages.shape) == (k_pages.shape[0], n_kv_heads, PAGE, vd) and v_pages.is_contiguous(),
+         "attention: bad cache page shape")
     if out is None:
-        out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
+    if vd != head_dim or softcap or slopes is not None:
+        need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
+             "attention: slopes must be float32 [heads]")
+        f = _f("attention_generic", "rf_attention_generic_ext", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+               c_void_p, c_int, c_int, c_void_p)
+        check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
+                ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
+                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), int(window or 0), T, stream()),
+              f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, v_head_dim={vd})")
+        return out
     f = _f("attention_generic", "rf_attention_generic", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
            c_void_p)
@@ -467,4 +485,216 @@ def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
             block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
             ptr(status_word(q.device)), stream()),
           f"attention_prefill_tc (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
+    return out
+
+
+def relu2(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """max(x, 0)^2 element by element (evaluated in 32-bit)."""
+    need_cuda(x)
+    need(x.is_contiguous(), "relu2: input must be contiguous")
+    if out is None:
+        out = torch.empty_like(x)
+    f = _f("elementwise", "rf_relu2", c_int, c_void_p, c_void_p, c_ll, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), ptr(out), x.numel(), stream()), "relu2")
+    return out
+
+
+def add_row(h: torch.Tensor, vec: torch.Tensor) -> None:
+    """h[t, :] += vec for every row of the float32 stream ``h``."""
+    need_cuda(h, vec)
+    need(h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous() and vec.shape == (h.shape[1],)
+         and vec.is_contiguous(), "add_row: h must be [T, H] float32 and vec [H]")
+    f = _f("elementwise", "rf_add_row", c_int, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(vec.dtype), ptr(h), ptr(vec), h.shape[0], h.shape[1], stream()), "add_row")
+
+
+def branch_norm_add(h: torch.Tensor, branches, post_weight: torch.Tensor, eps: float, compute_dtype: torch.dtype, *,
+                    extra: torch.Tensor | None = None, next_weight: torch.Tensor | None = None) -> torch.Tensor | None:
+    """The residual update of a block that norms its sub-layers' outputs, in 32-bit and in one pass over the rows:
+
+        m = a0                                    for branches == [(a0, None)]
+        m = (rms(a0) * w0 + rms(a1) * w1) / 2     for branches == [(a0, w0), (a1, w1)]
+        h += rms(m) * post_weight (+ extra)
+        returns rms(h) * next_weight in the compute dtype if ``next_weight`` is given, else None
+
+    with rms(x) = x / sqrt(mean(x^2) + eps).  The branches are float32 [T, H]; all weight vectors share one dtype.
+    """
+    need(len(branches) in (1, 2), "branch_norm_add: one or two branches")
+    a0, w0 = branches[0]
+    a1, w1 = branches[1] if len(branches) == 2 else (None, None)
+    need((len(branches) == 1) == (w0 is None), "branch_norm_add: two branches come with weights, one comes without")
+    vecs = [v for v in (w0, w1, post_weight, extra, next_weight) if v is not None]
+    need_cuda(h, a0, a1, *vecs)
+    T, H = h.shape
+    need(h.dtype == torch.float32 and h.is_contiguous(), "branch_norm_add: h must be contiguous float32 [T, H]")
+    for a in (a0, a1):
+        need(a is None or (a.dtype == torch.float32 and a.shape == (T, H) and a.is_contiguous()),
+             "branch_norm_add: a branch must be contiguous float32 [T, H]")
+    need(all(v.shape == (H,) and v.dtype == vecs[0].dtype and v.is_contiguous() for v in vecs)
+         and vecs[0].dtype in (torch.float32, torch.bfloat16), "branch_norm_add: weight vectors must be [H] of one dtype")
+    y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if next_weight is not None else None
+    f = _f("elementwise", "rf_branch_norm_add", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), ptr(w0), ptr(a1), ptr(w1), ptr(post_weight), ptr(extra),
+            ptr(next_weight), ptr(y), int(vecs[0].dtype == torch.float32), float(eps), T, H, stream()),
+          f"branch_norm_add (H={H})")
+    return y
+
+
+def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int,
+                       inv_freq: torch.Tensor | None, tok_seq, tok_pos, seq_slot, block_table: torch.Tensor,
+                       k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
+                       compute_dtype: torch.dtype | None = None, rot_dim: int = 0, interleaved: bool = False,
+                       unit_norm_eps: float | None = None) -> torch.Tensor:
+    """q | k | v rows on their way into the cache, for heads that are normed and for values of another size than keys.
+
+    ``qkv`` is [T, heads*head_dim + kv_heads*head_dim + kv_heads*v_head_dim] in the compute dtype, or a float32 stack
+    [S, T, ...] of partial sums.  With ``unit_norm_eps`` every query and key head is divided by its root mean square
+    (x / sqrt(mean(x^2) + eps), no weight) in 32-bit; then the first ``rot_dim`` elements turn (0: no rotation).
+    Returns q [T, heads*head_dim] in the compute dtype; k and v go to their pages.
+    """
+    need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages)
+    width = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
+    partials = qkv.dim() == 3
+    if partials:
+        need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] == width and compute_dtype is not None,
+             "head_norm_kv_write: partial sums must be a contiguous float32 [S, T, width] stack, with the compute dtype named")
+        S, T, dt, row_stride, pstride = qkv.shape[0], qkv.shape[1], compute_dtype, width, qkv.shape[1] * width
+    else:
+        need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == width, "head_norm_kv_write: qkv must be [T, width]")
+        S, T, dt, row_stride, pstride = 0, qkv.shape[0], qkv.dtype, qkv.stride(0), 0
+    need(rot_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2),
+         "head_norm_kv_write: inv_freq must hold rot_dim/2 float32 frequencies")
+    if write_kv:
+        need(k_pages is not None and k_pages.dtype == dt and k_pages.is_contiguous()
+             and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and v_pages is not None and v_pages.dtype == dt
+             and v_pages.is_contiguous() and tuple(v_pages.shape[1:]) == (n_kv_heads, PAGE, v_head_dim),
+             "head_norm_kv_write: pages must be [n_pages, kv_heads, 64, head size] of the compute dtype")
+    q_out = torch.empty((T, n_heads * head_dim), dtype=dt, device=qkv.device)
+    f = _f("elementwise", "rf_head_norm_kv_write", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
+           c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+           c_int, c_int, c_float, c_void_p)
+    check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(q_out), q_out.stride(0), n_heads, n_kv_heads, head_dim,
+            v_head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
+            ptr(k_pages), ptr(v_pages), int(write_kv), T, int(rot_dim), int(interleaved), int(unit_norm_eps is not None),
+            float(unit_norm_eps or 0.0), stream()), "head_norm_kv_write")
+    return q_out
+
+
+def gemm_simt_grouped(x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, tile_rows: int,
+                      n_rows: int, *, row_map: torch.Tensor | None = None, row_div: int = 1,
+                      out_f32: bool = False) -> torch.Tensor:
+    """One product for many weight matrices: y[r] = x[row_map[r] // row_div] @ w[group of r].T for the ``n_rows`` sorted
+    rows that the tile table lists (``kernels.moe_sort``); ``w`` is [groups, N, K]; without ``row_map`` row r reads x[r]."""
+    need_cuda(x, w, tiles, row_map)
+    need(x.dim() == 2 and w.dim() == 3 and x.dtype == w.dtype and x.stride(1) == 1 and w.is_contiguous()
+         and w.shape[2] == x.shape[1], "gemm_simt_grouped: x [M,K] and w [G,N,K] must share a dtype and K")
+    need(tiles.dtype == torch.int32 and tiles.numel() >= 1 + 3 * max_tiles, "gemm_simt_grouped: tile table too small")
+    need(row_map is None or (row_map.dtype == torch.int32 and row_map.numel() >= n_rows), "gemm_simt_grouped: bad row map")
+    G, N, K = w.shape
+    out = torch.empty((n_rows, N), dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
+    f = _f("gemm_simt", "rf_gemm_simt_grouped", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+           c_int, c_int, c_void_p, c_void_p, c_int, c_ll, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), ptr(w), ptr(out), max_tiles, tile_rows, N, K, x.stride(0), N, int(out_f32),
+            ptr(tiles), ptr(row_map), int(row_div), N * K, stream()), f"gemm_simt_grouped ({G} x {N}x{K})")
+    return out
+
+
+# ---------------------------------------------------------------- retention (csrc/retention.cu)
+
+def retention_prepare(proj: torch.Tensor, q_col: int, k_col: int, heads: int, dim: int, rot_dim: int,
+                      inv_freq: torch.Tensor | None, tok_pos: torch.Tensor, k_scale: float) -> torch.Tensor:
+    """q and k of the projection's rows (columns q_col.. and k_col.., heads*dim each) rotated by position in 32-bit
+    (first ``rot_dim`` elements of a head, pairs (i, i + rot_dim/2)), k times ``k_scale``: float32 [2, T, heads*dim]."""
+    need_cuda(proj, inv_freq, tok_pos)
+    need(proj.dim() == 2 and proj.stride(1) == 1, "retention_prepare: the projection must be [T, columns]")
+    need(rot_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2),
+         "retention_prepare: inv_freq must hold rot_dim/2 float32 frequencies")
+    T = proj.shape[0]
+    qk = torch.empty((2, T, heads * dim), dtype=torch.float32, device=proj.device)
+    f = _f("retention", "rf_retention_prepare", c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
+           c_void_p, c_void_p, c_float, c_int, c_void_p)
+    check(f(dtype_code(proj.dtype), ptr(proj), proj.stride(0), q_col, k_col, ptr(qk), heads, dim, rot_dim, ptr(inv_freq),
+            ptr(tok_pos), float(k_scale), T, stream()), "retention_prepare")
+    return qk
+
+
+def retention_scan(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, cu_q: torch.Tensor,
+                   seq_slot: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """S <- decay_h S + k v^T, o = S^T q, token by token for every sequence of the step; ``state`` [slots, heads, dim,
+    vdim] float32 is read at the step's start and left as after its last token.  ``v`` is a [T, heads*vdim] view (rows
+    may be strided).  Returns o float32 [T, heads*vdim]."""
+    need_cuda(qk, v, state, decay, cu_q, seq_slot)
+    T = qk.shape[1]
+    need(qk.dtype == torch.float32 and qk.is_contiguous() and qk.shape == (2, T, heads * dim), "retention_scan: bad q/k")
+    need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "retention_scan: v must be [T, heads*vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+         "retention_scan: state must be float32 [slots, heads, dim, vdim]")
+    need(decay.dtype == torch.float32 and decay.shape == (heads,), "retention_scan: decay must be float32 [heads]")
+    B = seq_slot.shape[0]
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qk.device)
+    f = _f("retention", "rf_retention_scan", c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(v.dtype), ptr(qk[0]), ptr(qk[1]), ptr(v), v.stride(0), ptr(state), ptr(decay), ptr(o), ptr(cu_q),
+            ptr(seq_slot), B, heads, dim, vdim, stream()), f"retention_scan (heads={heads}, dim={dim}, vdim={vdim})")
+    return o
+
+
+def retention_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float) -> torch.Tensor:
+    """o / sqrt(mean(o^2) + eps) per head, times silu(gate), in the gate's dtype."""
+    need_cuda(o, gate)
+    T = o.shape[0]
+    need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * vdim), "retention_gate: bad o")
+    need(gate.shape == (T, heads * vdim) and gate.stride(1) == 1, "retention_gate: gate must be [T, heads*vdim]")
+    out = torch.empty((T, heads * vdim), dtype=gate.dtype, device=o.device)
+    f = _f("retention", "rf_retention_gate", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
+    check(f(dtype_code(gate.dtype), ptr(o), ptr(gate), gate.stride(0), ptr(out), heads, vdim, float(eps), T, stream()),
+          "retention_gate")
+    return out
+
+
+# ---------------------------------------------------------------- routing of experts (csrc/moe.cu)
+
+MOE_TILE_SMALL, MOE_TILE_LARGE = 16, 64
+
+
+def moe_route(logits: torch.Tensor, top: int):
+    """(experts int32 [T, top], weights float32 [T, top]): the ``top`` largest router logits of every token (of equal
+    logits the lower index) and the softmax over those alone."""
+    need_cuda(logits)
+    need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "moe_route: logits must be float32 [T, E]")
+    T, E = logits.shape
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    f = _f("moe", "rf_moe_route", c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p)
+    check(f(ptr(logits), E, top, ptr(idx), ptr(w), T, stream()), f"moe_route (E={E}, top={top})")
+    return idx, w
+
+
+def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int):
+    """The (token, choice) pairs sorted by expert, on the device: (perm [n], inv [n], tiles, max_tiles); the tile table
+    lists (expert, first sorted row, end row) for row tiles of at most ``tile_rows`` rows that never span two experts."""
+    need_cuda(idx)
+    n = idx.numel()
+    max_tiles = (n + tile_rows - 1) // tile_rows + n_experts
+    dev = idx.device
+    perm = torch.empty((n,), dtype=torch.int32, device=dev)
+    inv = torch.empty((n,), dtype=torch.int32, device=dev)
+    offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
+    tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=dev)
+    f = _f("moe", "rf_moe_sort", c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
+    check(f(ptr(idx), n, n_experts, tile_rows, ptr(perm), ptr(inv), ptr(offsets), ptr(tiles), max_tiles, stream()),
+          f"moe_sort (E={n_experts})")
+    return perm, inv, tiles, max_tiles
+
+
+def moe_combine(y: torch.Tensor, inv: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_k w[t, k] * y[inv[t*top + k]] in the order of k; y float32 [T*top, H] in sorted order."""
+    need_cuda(y, inv, w)
+    T, top = w.shape
+    need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[0] == T * top, "moe_combine: y must be float32 [T*top, H]")
+    H = y.shape[1]
+    out = torch.empty((T, H), dtype=torch.float32, device=y.device)
+    f = _f("moe", "rf_moe_combine", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p)
+    check(f(ptr(y), ptr(inv), ptr(w), ptr(out), top, H, T, stream()), "moe_combine")
     return out

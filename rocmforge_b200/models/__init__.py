@@ -1,1 +1,2 @@
 from . import qwen2      # registers "Qwen2ForCausalLM"
+from . import rifizen    # registers "Rifizen"

@@ -7,3 +7,10 @@ from .attention import GQAAttention
 from .mlp import GatedMLP
 from .block import PreNormBlock
 from .embedding import TokenEmbedding, OutputHead
+from .base import NormedMean
+from .block import SandwichBlock
+from .mlp import SquaredReluMLP
+from .experts import RoutedExperts
+from .retention import Retention
+from .parallel import ParallelMixer
+from .offsets import PassOffsets

@@ -26,30 +26,55 @@ class GQAAttention(Mixer):
     (forward.rs:583); a query at position p sees keys 0..=p, or the last ``window`` of them.
     The three projections are fused into one matrix at load time (the reference fuses them
     in its decode kernels, src/gpu/ops.rs:748-880).
+
+    Options that other designs use, all off by default: ``v_head_dim`` (values of another size than keys),
+    ``qk_norm_eps`` (every query and key head divided by its root mean square, x / sqrt(mean(x^2) + eps), no weight,
+    before the rotation), ``softcap`` (score <- softcap * tanh(score / softcap) after scaling), ``distance_slopes``
+    (one slope per head: after the cap a score is lowered by slope * (query position - key position)), and ``names``
+    (the tensors' names below the part's prefix, keys q, k, v, o).  A mixer with any of the first four takes the
+    generic attention kernel, which knows them all.
     """
 
     accepts_scaled_rows = True
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  o_bias: bool = False, window: Optional[int] = None, position=None,
-                 scale: Optional[float] = None):
+                 scale: Optional[float] = None, v_head_dim: Optional[int] = None, qk_norm_eps: Optional[float] = None,
+                 softcap: Optional[float] = None, distance_slopes=None, names: Optional[Dict[str, str]] = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
         self.qkv_bias, self.o_bias, self.window = qkv_bias, o_bias, window
         self.position = position
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.v_head_dim = head_dim if v_head_dim is None else int(v_head_dim)
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.softcap = float(softcap) if softcap else None
+        self.distance_slopes = None if distance_slopes is None else [float(s) for s in distance_slopes]
+        if self.distance_slopes is not None and len(self.distance_slopes) != n_heads:
+            raise ValueError(f"{len(self.distance_slopes)} distance slopes for {n_heads} heads")
+        self.slopes_dev = None
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+        self.names.update(names or {})
         self.q_size = n_heads * head_dim
         self.kv_size = n_kv_heads * head_dim
+        self.v_size = n_kv_heads * self.v_head_dim
+        self.o_in = n_heads * self.v_head_dim
+        # what the tuned kernels do not know: these mixers use the generic attention and the per-head cache writer
+        self.plain_only = (self.v_head_dim != head_dim or self.qk_norm_eps is not None or self.softcap is not None
+                           or self.distance_slopes is not None)
+        if self.plain_only and (qkv_bias or o_bias):
+            raise ValueError("gqa_attention: biases do not go with normed heads, a score cap, distance slopes or another value size")
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
+        n = self.names
         s = {
-            "q_proj.weight": ParamSpec((self.q_size, self.hidden)),
-            "k_proj.weight": ParamSpec((self.kv_size, self.hidden)),
-            "v_proj.weight": ParamSpec((self.kv_size, self.hidden)),
-            "o_proj.weight": ParamSpec((self.hidden, self.q_size)),
+            n["q"]: ParamSpec((self.q_size, self.hidden)),
+            n["k"]: ParamSpec((self.kv_size, self.hidden)),
+            n["v"]: ParamSpec((self.v_size, self.hidden)),
+            n["o"]: ParamSpec((self.hidden, self.o_in)),
         }
         if self.qkv_bias:
             s["q_proj.bias"] = ParamSpec((self.q_size,), kind="vector")
@@ -60,16 +85,19 @@ class GQAAttention(Mixer):
         return s
 
     def bind(self, params, compute_dtype):
-        w = torch.cat([params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]], dim=0)
+        n = self.names
+        w = torch.cat([params[n["q"]], params[n["k"]], params[n["v"]]], dim=0)
         b = None
         if self.qkv_bias:
             bs = [params["q_proj.bias"], params["k_proj.bias"], params["v_proj.bias"]]
             dt = torch.float32 if any(x.dtype == torch.float32 for x in bs) else bs[0].dtype
             b = torch.cat([x.to(dt) for x in bs]).contiguous()
         self.qkv = Linear(w.contiguous(), b)
-        self.o = Linear(params["o_proj.weight"], params.get("o_proj.bias"))
+        self.o = Linear(params[n["o"]], params.get("o_proj.bias"))
         if self.position is not None:
             self.position.prepare(w.device)
+        if self.distance_slopes is not None:
+            self.slopes_dev = torch.tensor(self.distance_slopes, dtype=torch.float32, device=w.device)
 
     def cuda_modules(self, compute_dtype):
         mods = ["elementwise", "attention_generic"]
@@ -78,13 +106,14 @@ class GQAAttention(Mixer):
         return mods
 
     def cache_request(self):
-        return KVRequest(self.n_kv_heads, self.head_dim, self.window)
+        return KVRequest(self.n_kv_heads, self.head_dim, self.window,
+                         None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
     # rows of the query tiles of the two tiled prefill kernels (csrc/attention_prefill.cu, attention_prefill_tc.cu)
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        return tuple(self.TILE_ROWS)
+        return () if self.plain_only else tuple(self.TILE_ROWS)
 
     def step_table(self, name, batch):
         """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
@@ -102,6 +131,32 @@ class GQAAttention(Mixer):
         o = self.attend(ctx, q, cache_view)
         self.o.add_to_stream(ctx, o, stream)
 
+    def output(self, ctx, y, cache_view):
+        q = self.project_into_cache(ctx, y, cache_view)
+        return self.o(ctx, self.attend(ctx, q, cache_view), out_f32=True)
+
+    def _project_plain(self, ctx, y, view, rot, inv_freq):
+        """The projection for heads that are normed or values of another size: one product (K-split partial sums with
+        few tokens), then a warp per head norms, turns and writes."""
+        tc = kernels.tensor_core
+        w = self.qkv.weight
+        if isinstance(y, ScaledRows):
+            y = y.materialize()
+        common = dict(compute_dtype=ctx.compute_dtype, rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False),
+                      unit_norm_eps=self.qk_norm_eps)
+        args = (self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim, inv_freq, ctx.tok_seq, ctx.tok_pos,
+                ctx.seq_slot, view.block_table, view.k_pages, view.v_pages, view.writes)
+        if y.shape[0] <= tc.SKINNY_MAX_TOKENS:
+            if ctx.uses_tensor_cores(y, w, tc.PARTIAL):
+                splits = tc.split_k_for(w.shape[0], w.shape[1], tokens=y.shape[0])
+                if splits > 1:
+                    return kernels.head_norm_kv_write(tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits), *args, **common)
+            elif not ctx.uses_tensor_cores(y, w, tc.STORE):
+                splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
+                if splits > 1:
+                    return kernels.head_norm_kv_write(kernels.gemm_simt(y, w, splits=splits), *args, **common)
+        return kernels.head_norm_kv_write(ctx.matmul(y, w), *args, **common)
+
     def project_into_cache(self, ctx, y, view):
         """q/k/v projection (+ bias), rotation, cache write; returns rotated q [T, >= heads*head_dim].
 
@@ -114,6 +169,8 @@ class GQAAttention(Mixer):
         y, row_ss = ctx.unpack_rows(y, w, tc.PARTIAL)
         rot = dict((self.position.rotation() if self.position is not None else None) or dict(inv_freq=None, rot_dim=0))
         inv_freq = rot.pop("inv_freq")
+        if self.plain_only:
+            return self._project_plain(ctx, y, view, rot, inv_freq)
         rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot,
                     block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
         if y.shape[0] <= tc.SKINNY_MAX_TOKENS and ctx.uses_tensor_cores(y, w, tc.PARTIAL):
@@ -141,6 +198,10 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         tiles64, tiles128 = ctx.tables.get("attention_tiles64"), ctx.tables.get("attention_tiles128")
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
+        if self.plain_only:
+            return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
+                                             ctx.seq_slot, view.block_table, self.scale, view.window,
+                                             v_head_dim=self.v_head_dim, softcap=self.softcap, slopes=self.slopes_dev)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
             if ctx.options.clustered_decode:

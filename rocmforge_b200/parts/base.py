@@ -96,6 +96,20 @@ class Mixer(Part):
     def forward(self, ctx, y: torch.Tensor, cache_view, stream) -> None:
         raise NotImplementedError
 
+    def output(self, ctx, y: torch.Tensor, cache_view):
+        """The mixer's result as float32 [T, H] instead of an update of the stream, for blocks that do something to
+        it first (norm it, merge it with another mixer's).  A mixer that offers only ``forward`` cannot sit in those."""
+        raise NotImplementedError(f"{type(self).__name__} does not hand out its result (only forward)")
+
+
+class NormedMean:
+    """A sub-layer's result that is still to be formed: the mean of ``branches`` = [(float32 [T, H], weight [H])],
+    each first RMS-normed over the width with its weight and ``eps``.  Whoever adds it to the stream forms it in the
+    same pass (kernels.branch_norm_add)."""
+
+    def __init__(self, branches, eps: float):
+        self.branches, self.eps = list(branches), float(eps)
+
 
 class FeedForward(Part):
     """Position-wise transformation (dense here; routed experts would live behind the same face)."""
@@ -104,6 +118,10 @@ class FeedForward(Part):
 
     def forward(self, ctx, y: torch.Tensor, stream) -> None:
         raise NotImplementedError
+
+    def output(self, ctx, y: torch.Tensor) -> torch.Tensor:
+        """The result as float32 [T, H] instead of an update of the stream (see Mixer.output)."""
+        raise NotImplementedError(f"{type(self).__name__} does not hand out its result (only forward)")
 
 
 class Block(Part):

@@ -35,3 +35,73 @@ class PreNormBlock(Block):
         stream.next_norm = after
         self.ffn.forward(ctx, y, stream)
         stream.next_norm = None
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))): every sub-layer is normed on its way in and on its way
+    out.  ``ffn`` (with norm2 and post2) may be None: the block is then its first half.
+
+    The outputs of the sub-layers, their norms and the sums are 32-bit.  One kernel per sub-layer forms the mixer's
+    merge (if it hands out a ``NormedMean``), the out-norm, the sum into the stream, a row vector that the schedule
+    adds after the block (``stream.after_extra``) and the norm that reads the stream next, which therefore never
+    launches on its own.
+    """
+
+    def __init__(self, norm1: Norm, mixer: Mixer, post1: Norm, norm2: Norm = None, ffn: FeedForward = None,
+                 post2: Norm = None, names: Dict[str, str] = None):
+        if (ffn is None) != (norm2 is None) or (ffn is None) != (post2 is None):
+            raise ValueError("sandwich block: norm2, ffn and post2 come together or not at all")
+        self.norm1, self.mixer, self.post1 = norm1, mixer, post1
+        self.norm2, self.ffn, self.post2 = norm2, ffn, post2
+        self.names = dict(names)
+
+    def sub_parts(self) -> Dict[str, Part]:
+        out = {self.names["norm1"]: self.norm1, self.names["post1"]: self.post1}
+        if hasattr(self.mixer, "leaf_parts"):                # a mixer made of mixers: its halves have prefixes of their own
+            for sub, part in self.mixer.leaf_parts().items():
+                out[self.names["mixer"] + sub] = part
+        else:
+            out[self.names["mixer"]] = self.mixer
+        if self.ffn is not None:
+            out.update({self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn, self.names["post2"]: self.post2})
+        return out
+
+    def entry_norm(self):
+        return self.norm1
+
+    @staticmethod
+    def _add(ctx, stream, result, post, next_norm, extra):
+        """stream += post(result) (+ extra); leaves ``next_norm`` of the new stream prepared if it is a plain RMS norm
+        of the same eps."""
+        from .. import kernels
+        from .base import NormedMean
+        weight, eps = post.deferred_params()
+        if isinstance(result, NormedMean):
+            if result.eps != eps:
+                raise NotImplementedError("sandwich block: the merge and the out-norm must share eps")
+            branches = result.branches
+        else:
+            branches = [(result, None)]
+        nxt = next_norm.deferred_params() if next_norm is not None else None
+        if nxt is not None and nxt[1] != eps:
+            nxt = None
+        stream.flush()
+        stream.prepared = None
+        y = kernels.branch_norm_add(stream.h, branches, weight, eps, ctx.compute_dtype, extra=extra,
+                                    next_weight=nxt[0] if nxt is not None else None)
+        if y is not None:
+            stream.prepared = (next_norm, y)
+
+    def forward(self, ctx, stream, cache_view):
+        after, extra = stream.after_block, stream.after_extra
+        stream.after_extra = None                    # added here, with the block's last update
+        stream.next_norm = None
+        y = self.norm1.forward(ctx, stream)
+        r = self.mixer.output(ctx, y, cache_view)
+        if self.ffn is None:
+            self._add(ctx, stream, r, self.post1, after, extra)
+            return
+        self._add(ctx, stream, r, self.post1, self.norm2, None)
+        y = self.norm2.forward(ctx, stream)
+        self._add(ctx, stream, self.ffn.output(ctx, y), self.post2, after, extra)

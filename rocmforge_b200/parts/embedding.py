@@ -14,15 +14,15 @@ from .linear import Linear
 class TokenEmbedding(Part):
     """x = E[token], no scaling (maeddesg/ROCmForge src/gpu/forward.rs:826-883)."""
 
-    def __init__(self, vocab: int, hidden: int):
-        self.vocab, self.hidden = vocab, hidden
+    def __init__(self, vocab: int, hidden: int, param_name: str = "weight"):
+        self.vocab, self.hidden, self.param_name = vocab, hidden, param_name
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.vocab, self.hidden))}
+        return {self.param_name: ParamSpec((self.vocab, self.hidden))}
 
     def bind(self, params, compute_dtype):
-        self.weight = params["weight"]
+        self.weight = params[self.param_name]
 
     def cuda_modules(self, compute_dtype):
         return ["elementwise"]
@@ -35,15 +35,15 @@ class OutputHead(Part):
     """logits = W y in float32; with tied embeddings W is the embedding matrix itself
     (maeddesg/ROCmForge src/gpu/forward.rs:1313-1338; tie: src/gpu/weights.rs:868-886)."""
 
-    def __init__(self, vocab: int, hidden: int, tied_to: Optional[str] = None):
-        self.vocab, self.hidden, self.tied_to = vocab, hidden, tied_to
+    def __init__(self, vocab: int, hidden: int, tied_to: Optional[str] = None, param_name: str = "weight"):
+        self.vocab, self.hidden, self.tied_to, self.param_name = vocab, hidden, tied_to, param_name
         self.linear: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.vocab, self.hidden), tied_to=self.tied_to)}
+        return {self.param_name: ParamSpec((self.vocab, self.hidden), tied_to=self.tied_to)}
 
     def bind(self, params, compute_dtype):
-        self.linear = Linear(params["weight"])
+        self.linear = Linear(params[self.param_name])
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         return self.linear(ctx, y, out_f32=True)

@@ -1,0 +1,78 @@
+"""A feed-forward made of many small ones, of which every token uses a few."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels
+from ..engine.stream import ScaledRows
+from ..weights.spec import ParamSpec
+from .base import FEED_FORWARDS, FeedForward
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """z = W_router y + b in 32-bit; a token uses the ``top`` experts with the largest z, weighted by the softmax over
+    those z alone; an expert is W_down (silu(W_gate y) * (W_up y)) without biases; the result is the weighted sum.
+
+    Nothing of the routing reaches the host.  The (token, choice) pairs are sorted by expert on the device, one grouped
+    product over the sorted rows serves gate and up of all experts (the experts' matrices are stacked at load time, gate
+    and up interleaved row by row), one the down projections, and the choices of a token are summed in the order of the
+    choices, in 32-bit: a token's result does not depend on the rest of the batch.
+    Tensors: ``router`` [E, H], ``router.b`` [E], ``e<i>.gate`` / ``.up`` [F, H], ``e<i>.down`` [H, F]
+    (``names`` may rename router, router_bias, gate, up, down; ``expert_prefix`` the "e").
+    """
+
+    def __init__(self, hidden: int, intermediate: int, n_experts: int, top: int, *, router_bias: bool = True,
+                 names: Optional[Dict[str, str]] = None, expert_prefix: str = "e"):
+        if not 1 <= top <= n_experts:
+            raise ValueError(f"routed experts: top {top} of {n_experts} experts")
+        self.hidden, self.intermediate, self.n_experts, self.top = hidden, intermediate, n_experts, top
+        self.router_bias = router_bias
+        self.names = {"router": "router", "router_bias": "router.b", "gate": "gate", "up": "up", "down": "down"}
+        self.names.update(names or {})
+        self.expert_prefix = expert_prefix
+        self.router_w = self.router_b = self.gate_up = self.down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.expert_prefix}{e}.{self.names[which]}"
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s = {self.names["router"]: ParamSpec((self.n_experts, self.hidden))}
+        if self.router_bias:
+            s[self.names["router_bias"]] = ParamSpec((self.n_experts,), kind="vector", init="zeros")
+        for e in range(self.n_experts):
+            s[self._expert(e, "gate")] = ParamSpec((self.intermediate, self.hidden))
+            s[self._expert(e, "up")] = ParamSpec((self.intermediate, self.hidden))
+            s[self._expert(e, "down")] = ParamSpec((self.hidden, self.intermediate))
+        return s
+
+    def bind(self, params, compute_dtype):
+        self.router_w = params[self.names["router"]]
+        self.router_b = params[self.names["router_bias"]].to(torch.float32) if self.router_bias else None
+        E, F, H = self.n_experts, self.intermediate, self.hidden
+        gu = torch.stack([torch.stack([params[self._expert(e, "gate")], params[self._expert(e, "up")]], dim=1)
+                          for e in range(E)])                                # [E, F, 2, H]: row 2j = gate_j, 2j+1 = up_j
+        self.gate_up = gu.reshape(E, 2 * F, H).contiguous()
+        self.down = torch.stack([params[self._expert(e, "down")] for e in range(E)]).contiguous()      # [E, H, F]
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise", "gemm_simt", "moe"]
+
+    def output(self, ctx, y):
+        if isinstance(y, ScaledRows):
+            y = y.materialize()
+        T = y.shape[0]
+        z = kernels.gemm_simt(y, self.router_w, self.router_b, out_f32=True)                 # 32-bit sums, any shape
+        idx, w = kernels.moe_route(z, self.top)
+        rows = kernels.MOE_TILE_SMALL if T * self.top <= 16 * self.n_experts else kernels.MOE_TILE_LARGE
+        perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
+        n = T * self.top
+        gu = kernels.gemm_simt_grouped(y, self.gate_up, tiles, max_tiles, rows, n, row_map=perm, row_div=self.top)
+        a = kernels.swiglu(gu)                                                               # [n, F], sorted rows
+        d = kernels.gemm_simt_grouped(a, self.down, tiles, max_tiles, rows, n, out_f32=True)
+        return kernels.moe_combine(d, inv, w)
+
+    def forward(self, ctx, y, stream):
+        stream.add_pending(self.output(ctx, y))

@@ -50,3 +50,41 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, y, stream):
         a = ctx.gated_activation(y, self.gate_up)                           # [T, I]
         self.down.add_to_stream(ctx, a, stream)
+
+    def output(self, ctx, y):
+        return self.down(ctx, ctx.gated_activation(y, self.gate_up), out_f32=True)
+
+
+@FEED_FORWARDS.register("relu2_mlp")
+class SquaredReluMLP(FeedForward):
+    """W_down relu(W_up y)^2, no gate, no biases.  ``names``: the tensors' names below the part's prefix (up, down)."""
+
+    def __init__(self, hidden: int, intermediate: int, names: Optional[Dict[str, str]] = None):
+        self.hidden, self.intermediate = hidden, intermediate
+        self.names = {"up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.names["up"]: ParamSpec((self.intermediate, self.hidden)),
+                self.names["down"]: ParamSpec((self.hidden, self.intermediate))}
+
+    def bind(self, params, compute_dtype):
+        self.up = Linear(params[self.names["up"]])
+        self.down = Linear(params[self.names["down"]])
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
+    def activated(self, ctx, y):
+        from ..engine.stream import ScaledRows
+        if isinstance(y, ScaledRows):
+            y = y.materialize()
+        return kernels.relu2(self.up(ctx, y))
+
+    def forward(self, ctx, y, stream):
+        self.down.add_to_stream(ctx, self.activated(ctx, y), stream)
+
+    def output(self, ctx, y):
+        return self.down(ctx, self.activated(ctx, y), out_f32=True)

@@ -16,17 +16,19 @@ class RMSNorm(Norm):
     after normalisation and is used as stored (no 1 + w)
     (maeddesg/ROCmForge hip_kernels/norm.hip:18-84, src/cpu/ops.rs:32-46)."""
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, param_name: str = "weight"):
+        """``param_name``: the weight's name below the part's prefix ("" where the prefix is the tensor's whole name)."""
         self.size = size
         self.eps = float(eps)
+        self.param_name = param_name
         self.weight: Optional[torch.Tensor] = None
         self.compute_dtype = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), kind="vector", init="ones")}
+        return {self.param_name: ParamSpec((self.size,), kind="vector", init="ones")}
 
     def bind(self, params, compute_dtype):
-        self.weight = params["weight"]
+        self.weight = params[self.param_name]
         self.compute_dtype = compute_dtype
 
     def cuda_modules(self, compute_dtype):
@@ -39,6 +41,8 @@ class RMSNorm(Norm):
         prepared, stream.prepared = stream.prepared, None
         if prepared is not None and prepared[0] is self and rows is None and stream.pending is None:
             # the product that updated the stream has multiplied by this norm's weight and left the sums of squares
+            if isinstance(prepared[1], torch.Tensor):      # whoever updated the stream has run this norm as well
+                return prepared[1]
             return prepared[1] if deferred_ok else prepared[1].materialize()
         y = kernels.add_rmsnorm(stream.h, self.weight, self.eps, self.compute_dtype,
                                 pending=stream.pending, rows=rows)
