@@ -378,6 +378,106 @@ def prefill_rate(model, tokens, repeats, seed):
     return times[len(times) // 2]
 
 
+# ---------------------------------------------------------------- the Rifizen design beside the dense decoder (--only rifizen)
+
+def rifizen_shape(width, layers=4):
+    """A Rifizen configuration with layers of the size a real model has: 128-element heads, a window of 1,024, a
+    state of 128 x 128 per retention head, a dense feed-forward of 4 x width and 16 experts of width each (2 per token),
+    alternating.  And the dense decoder of equal width, heads and depth, whose gated feed-forward has as many weights."""
+    heads = width // 128
+    left = dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, mask={"size": 1024}, scale=128 ** -0.5, softcap=30.0)
+    right = dict(heads=heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** -(5 + 7 * h / max(1, heads - 1)) for h in range(heads)],
+                 rot=dict(dims=128, base=1e6))
+    dense = dict(kind="dense", ff=4 * width)
+    moe = dict(kind="moe", expert=dict(ff=width), router=dict(experts=16, top=2))
+    rif = dict(architecture="Rifizen", vocab=32000, width=width, norm=dict(eps=1e-6),
+               layers=[dict(type="parallel", mixer=dict(left=left, right=right), mlp=dense if i % 2 == 0 else moe)
+                       for i in range(layers)])
+    qwen = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), head_dim=128, intermediate_size=width * 8 // 3 // 128 * 128,
+                vocab_size=32000, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False,
+                max_position_embeddings=8192)
+    return rif, qwen
+
+
+def kernel_table(fn, top=14):
+    """[(kernel name, launches, device microseconds)] of one call of ``fn``, heaviest first (torch's profiler; the
+    times are those of the kernels in place, one after the other on the stream)."""
+    import ctypes
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from rocmforge_b200.csrc import build
+    fn()
+    torch.cuda.synchronize()
+
+    def dependent_launch(on):
+        # with programmatic dependent launch a kernel starts while its predecessor runs and waits for it: its duration
+        # would count the predecessor's.  Off for the table, so that a kernel's time is its own.
+        for lib in build._loaded.values():
+            if hasattr(lib, "rf_set_pdl"):
+                lib.rf_set_pdl(ctypes.c_int(1 if on else 0))
+    dependent_launch(False)
+    try:
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+    finally:
+        dependent_launch(os.environ.get("ROCMFORGE_B200_PDL", "1") != "0")
+    rows = []
+    for e in prof.key_averages():
+        us = getattr(e, "self_device_time_total", None)
+        if us is None:
+            us = getattr(e, "self_cuda_time_total", 0.0)
+        if us > 0:
+            rows.append((e.key[:70], int(e.count), round(float(us), 1)))
+    rows.sort(key=lambda r: -r[2])
+    return rows[:top]
+
+
+def rifizen_points(pk, seed, widths=(1024, 2048), tokens=PREFILL_TOKENS, batches=(8, 64), steps=64, warmup=8):
+    """Prefill and decode of the Rifizen design at layer sizes of a real model, beside the dense decoder at equal
+    size, with the heaviest kernels of each step."""
+    import torch
+    import rocmforge_b200 as rf
+    from rocmforge_b200 import StepRequest
+    from rocmforge_b200.config import architecture_for
+    out = {}
+    for width in widths:
+        point = {}
+        for name, raw in zip(("rifizen", "dense"), rifizen_shape(width)):
+            arch = architecture_for("Rifizen" if name == "rifizen" else "Qwen2ForCausalLM")
+            cfg = arch.config_cls.from_dict(raw)
+            model = rf.Model.random(cfg, seed=seed, dtype=torch.bfloat16)
+            V = model.spec.vocab_size
+            ms = prefill_rate(model, tokens, 4, seed + 2)
+            r = {"weights_MB": round(model.weight_bytes / 1e6, 1), "prefill_ms": round(ms, 3), "prefill_tok_s": round(tokens / (ms / 1e3), 1)}
+            cache = model.new_cache(max_tokens=tokens + 64, max_slots=2)
+            prompt = random_prompts(1, tokens, V, seed)[0]
+
+            def one_prompt():
+                s = cache.alloc_slot()
+                model.step(cache, [StepRequest(s, prompt, [tokens - 1])])
+                cache.free_slot(s)
+            r["prefill_kernels"] = kernel_table(one_prompt)
+            del cache
+            for b in batches:
+                d = decode_rate(model, random_prompts(b, PROMPT_LEN, V, seed + b), steps, warmup, check=4)
+                r[f"decode_b{b}_ms"] = round(d["ms_per_step"], 4)
+                r[f"decode_b{b}_tok_s"] = round(d["tok_s"], 1)
+            cache = model.new_cache(max_tokens=batches[0] * (PROMPT_LEN + 64), max_slots=batches[0])
+            slots = [cache.alloc_slot() for _ in range(batches[0])]
+            prefill_prompts(model, cache, slots, random_prompts(batches[0], PROMPT_LEN, V, seed + 1))
+
+            def one_decode():
+                model.step(cache, [StepRequest(s, [1], [0]) for s in slots])
+            r[f"decode_b{batches[0]}_kernels"] = kernel_table(one_decode)
+            del cache, model
+            torch.cuda.empty_cache()
+            point[name] = r
+        out[f"width{width}"] = point
+    return out
+
+
 def other_shapes(pk, seed, only=None):
     """BASELINE.json's two further configurations, as flat numbers for ``points``: the 0.5B shape in bfloat16 and in
     true 32-bit (a batch of 64 with prompt lengths uniform in 16..1,024, 256 decode steps; device-timed, its share of
@@ -445,7 +545,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
                     help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
@@ -469,6 +569,11 @@ def main():
     from rocmforge_b200.config import Qwen2Config
 
     pk = peaks()
+    if args.only == "rifizen":
+        print(json.dumps({"only": "rifizen", "tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
+                          "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
+                          **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup)}))
+        return 0
     if args.only in ("0.5b", "14b"):
         print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))
         return 0

@@ -86,7 +86,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tiles, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, const int* __restrict__ seq_nnew,
                             const int* __restrict__ cu_q, const int* __restrict__ block_table, int max_pages,
-                            int nh, int nkv, float scale, int window, int* __restrict__ status) {
+                            int nh, int nkv, float scale, int window, int* __restrict__ status, float softcap,
+                            const float* __restrict__ slopes) {
     constexpr int HALVES = HD / 64;                     // 128-byte column blocks of a head
     constexpr uint32_t QH_BYTES = AT_BM * 128;          // one column block of the Q tile (also the P tile)
     constexpr uint32_t Q_BYTES = HALVES * QH_BYTES;
@@ -224,7 +225,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int pos_i = pos_first + row;
         const int lo_i = (window > 0 && pos_i - window + 1 > 0) ? pos_i - window + 1 : 0;
         const bool row_ok = row < rows_here;
-        const float sl2 = scale * 1.4426950408889634f;
+        // designs that cap their scores (softcap * tanh(score / softcap)) and lower them by slope * distance: the row of
+        // scores is transformed in registers before the softmax (32-bit), and the exponent's factor is log2 e alone
+        const bool ext = softcap > 0.f || slopes != nullptr;
+        const float slope = slopes != nullptr ? slopes[head] : 0.f;
+        const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+        const float sl2 = (ext ? 1.f : scale) * 1.4426950408889634f;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int t = 0; t < n_kt; ++t) {
@@ -261,6 +267,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tcgen05_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) sc[c0 + j] = __uint_as_float(r[j]);
+                }
+            }
+            if (ext) {
+                const float dist0 = (float)(pos_i - key0);
+#pragma unroll
+                for (int j = 0; j < AT_BN; ++j) {
+                    float v = sc[j] * scale;
+                    if (softcap > 0.f) {
+                        // tanh(x) = 1 - 2 / (1 + e^(2x)): exact at both ends (e^(2x) = inf or 0), absolute error 1e-7 in between
+                        const float e2 = at_exp2(v * inv_cap * 2.8853900817779268f);
+                        v = softcap * (1.f - __fdividef(2.f, 1.f + e2));
+                    }
+                    sc[j] = fmaf(-slope, dist0 - (float)j, v);
                 }
             }
             if (!no_mask) {
@@ -367,7 +386,7 @@ template <int HD>
 static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, int out_stride,
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
-                     int* status, cudaStream_t st) {
+                     int* status, float softcap, const float* slopes, cudaStream_t st) {
     constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 15 * 8 + 16;
     static bool configured = false;
     if (!configured) {
@@ -378,7 +397,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     }
     cudaError_t e = rf_launch(attention_prefill_tc_kernel<HD>, dim3(nh, n_tiles), dim3(AT_THREADS), smem, st, mq, mk, mv,
                               reinterpret_cast<__nv_bfloat16*>(out), out_stride, tiles, seq_slot, seq_start, seq_nnew, cu_q,
-                              block_table, max_pages, nh, nkv, scale, window, status);
+                              block_table, max_pages, nh, nkv, scale, window, status, softcap, slopes);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -393,11 +412,13 @@ int rf_attention_prefill_tc_supported(int nh, int nkv, int hd) {
 
 // tiles: n_tiles pairs (sequence index, first new-token row of the tile within the sequence), 128 rows a tile.
 // q: [T, q_stride] with the heads' columns first; T is needed for the map's extent.
-int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
-                            const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
-                            const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
-                            int max_pages, int nh, int nkv, int hd, float scale, int window, int* status,
-                            cudaStream_t st) {
+// softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
+// lowered by slopes[head] * (query position - key position).
+int rf_attention_prefill_tc_ext(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
+                                const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
+                                const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
+                                int max_pages, int nh, int nkv, int hd, float scale, int window, float softcap,
+                                const float* slopes, int* status, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     if (n_tiles > 65535) return RF_ERR_UNSUPPORTED;      // tiles are the grid's y dimension (8 million prompt tokens)
     if (!rf_attention_prefill_tc_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
@@ -410,9 +431,19 @@ int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int o
         return e;
     if (hd == 64)
         return at_launch<64>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                             max_pages, nh, nkv, scale, window, status, st);
+                             max_pages, nh, nkv, scale, window, status, softcap, slopes, st);
     return at_launch<128>(mq, mk, mv, out, out_stride, tiles, n_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table,
-                          max_pages, nh, nkv, scale, window, status, st);
+                          max_pages, nh, nkv, scale, window, status, softcap, slopes, st);
+}
+
+int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
+                            const void* v_pages, long long n_pages, const int* tiles, int n_tiles, const int* seq_slot,
+                            const int* seq_start, const int* seq_nnew, const int* cu_q, const int* block_table,
+                            int max_pages, int nh, int nkv, int hd, float scale, int window, int* status,
+                            cudaStream_t st) {
+    return rf_attention_prefill_tc_ext(q, q_stride, T, out, out_stride, k_pages, v_pages, n_pages, tiles, n_tiles, seq_slot,
+                                       seq_start, seq_nnew, cu_q, block_table, max_pages, nh, nkv, hd, scale, window, 0.f,
+                                       nullptr, status, st);
 }
 
 }

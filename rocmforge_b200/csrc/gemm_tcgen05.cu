@@ -30,10 +30,16 @@
 // NORM = true (weights-as-rows only): the variant that applies a deferred norm to its input rows (pn.ss_in)
 // and/or finishes the residual update and prepares the next norm (EPI_RESNORM); it needs more registers, so the
 // ordinary products do not carry it.
-template <int BN, bool SWAP, int STAGES, bool NORM = false>
+// GROUPED = true (tokens as rows only): one launch for many weight matrices, the experts of a routed feed-forward.
+// Row tile y of the grid is (group, first row, end row) of grp.tiles (grp.tiles[0] tiles exist; the others return at
+// once); its rows of X, sorted by group, meet rows group * group_n + ... of the stacked weights W [groups * group_n, K];
+// rows of the tile beyond its end belong to the next group and are computed but not stored.
+template <int BN, bool SWAP, int STAGES, bool NORM = false, bool GROUPED = false>
 __global__ void __launch_bounds__(TC_THREADS, SWAP ? (STAGES <= 4 && BN == 16 ? 3 : 2) : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p,
-               typename std::conditional<NORM, TcNorm, TcNoNorm>::type norm_arg) {
+               typename std::conditional<NORM, TcNorm, TcNoNorm>::type norm_arg,
+               typename std::conditional<GROUPED, TcGroup, TcNoNorm>::type grp_arg) {
+    static_assert(!(GROUPED && (SWAP || NORM)), "grouped products are tokens-as-rows and carry no norm");
     // the variant without the norm never looks at this (every use below sits behind ``NORM &&``)
     const TcNorm& pn = *reinterpret_cast<const TcNorm*>(&norm_arg);
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -52,6 +58,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.y, tile_b = blockIdx.x, split = blockIdx.z;
+    int coord_a = tile_a * TC_BM, coord_b = tile_b * BN;            // first rows of the two operands' tiles
+    if constexpr (GROUPED) {
+        const TcGroup& grp = *reinterpret_cast<const TcGroup*>(&grp_arg);
+        pdl_wait();                                     // the tile table is the sorting kernel's
+        if (tile_a >= grp.tiles[0]) return;             // the whole CTA, before it owns anything
+        const int* tl = grp.tiles + 1 + 3 * tile_a;
+        coord_b = tl[0] * grp.group_n + tile_b * BN;
+        coord_a = tl[1];
+        p.M = tl[2];                                    // rows from here on are another group's
+    }
     const int kb_total = (p.K + TC_BK - 1) / TC_BK;
     const int kb_begin = split * p.k_blocks_per_split;
     int kb_end = kb_begin + p.k_blocks_per_split;
@@ -89,16 +105,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(full, STAGE_BYTES);
                 const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
                 const int k0 = (kb_begin + i) * TC_BK;
-                if (SWAP) tma_load_2d(sa, &map_a, k0, tile_a * TC_BM, full);
-                else tma_load_2d(sa + A_BYTES, &map_b, k0, tile_b * BN, full);
+                if (SWAP) tma_load_2d(sa, &map_a, k0, coord_a, full);
+                else tma_load_2d(sa + A_BYTES, &map_b, k0, coord_b, full);
             }
             pdl_wait();
             for (int i = 0; i < pre; ++i) {
                 const uint32_t full = smem_u32(&bars[i]);
                 const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
                 const int k0 = (kb_begin + i) * TC_BK;
-                if (SWAP) tma_load_2d(sa + A_BYTES, &map_b, k0, tile_b * BN, full);
-                else tma_load_2d(sa, &map_a, k0, tile_a * TC_BM, full);
+                if (SWAP) tma_load_2d(sa + A_BYTES, &map_b, k0, coord_b, full);
+                else tma_load_2d(sa, &map_a, k0, coord_a, full);
             }
             for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
@@ -108,8 +124,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(full, STAGE_BYTES);
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                 const int k0 = (kb_begin + i) * TC_BK;
-                tma_load_2d(sa, &map_a, k0, tile_a * TC_BM, full);
-                tma_load_2d(sa + A_BYTES, &map_b, k0, tile_b * BN, full);
+                tma_load_2d(sa, &map_a, k0, coord_a, full);
+                tma_load_2d(sa + A_BYTES, &map_b, k0, coord_b, full);
             }
         }
     } else if (warp == 1) {
@@ -151,7 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, &abort_flag);
         tcgen05_fence_after();
         if (ok && n_kb > 0 && !(NORM && p.mode == EPI_RESNORM)) {
-            const int row_a = tile_a * TC_BM + quarter * 32 + lane;        // index along map A's rows
+            const int row_a = coord_a + quarter * 32 + lane;               // index along map A's rows
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             constexpr int CH = BN < 32 ? 16 : 32;
 #pragma unroll 1
@@ -299,19 +315,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-template <int BN, bool SWAP, int STAGES, bool NORM = false>
+template <int BN, bool SWAP, int STAGES, bool NORM = false, bool GROUPED = false>
 static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t st,
-                      const TcNorm* norm = nullptr, int cluster_z = 1) {
+                      const TcNorm* norm = nullptr, int cluster_z = 1, const TcGroup* group = nullptr) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, STAGES, NORM>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, STAGES, NORM, GROUPED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     typename std::conditional<NORM, TcNorm, TcNoNorm>::type extra{};
     if constexpr (NORM) extra = *norm;
+    typename std::conditional<GROUPED, TcGroup, TcNoNorm>::type grp{};
+    if constexpr (GROUPED) grp = *group;
     if (cluster_z > 1) {                             // the K splits of a tile as one cluster
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
@@ -325,12 +343,12 @@ static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = g_rf_pdl ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAP, STAGES, NORM>, ma, mb, p, extra);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAP, STAGES, NORM, GROUPED>, ma, mb, p, extra, grp);
         if (e != cudaSuccess) return (int)e;
         RF_LAUNCH_CHECK();
         return 0;
     }
-    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM>, grid, dim3(TC_THREADS), smem, st, ma, mb, p, extra);
+    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM, GROUPED>, grid, dim3(TC_THREADS), smem, st, ma, mb, p, extra, grp);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -360,6 +378,27 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
     if ((e = make_map(&ma, X, M, K, ldx, TC_BM)) || (e = make_map(&mb, W, N, K, K, 128))) return e;
     dim3 grid((N + 127) / 128, (M + TC_BM - 1) / TC_BM, 1);
     return launch_cfg<128, false, 6>(ma, mb, p, grid, st);
+}
+
+// Many weight matrices in one launch (see GROUPED above): X [n_rows, K] holds the rows sorted by group, W [groups, N, K]
+// the stacked weights, tiles the table of row tiles of at most 128 rows (max_tiles of them at most); out [n_rows, N]
+// (mode STORE / F32) or [n_rows, N/2] (SWIGLU on row-interleaved gate/up weights).
+int rf_gemm_tc_grouped(const void* X, int ldx, int n_rows, const void* W, int groups, int N, int K, void* out, int ldo,
+                       int mode, const int* tiles, int max_tiles, int* status, cudaStream_t st) {
+    if (n_rows <= 0 || max_tiles <= 0) return 0;
+    if (!rf_gemm_tc_supported(n_rows, N, K, mode) || (mode != EPI_STORE && mode != EPI_F32 && mode != EPI_SWIGLU))
+        return RF_ERR_UNSUPPORTED;
+    if (max_tiles > 65535) return RF_ERR_UNSUPPORTED;
+    CUtensorMap ma, mb;
+    int e;
+    TcParams p{out, nullptr, 0, n_rows, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
+    const TcGroup grp{tiles, N};
+    if (N > 128) {
+        if ((e = make_map(&ma, X, n_rows, K, ldx, TC_BM)) || (e = make_map(&mb, W, (long long)groups * N, K, K, 256))) return e;
+        return launch_cfg<256, false, 4, false, true>(ma, mb, p, dim3((N + 255) / 256, max_tiles, 1), st, nullptr, 1, &grp);
+    }
+    if ((e = make_map(&ma, X, n_rows, K, ldx, TC_BM)) || (e = make_map(&mb, W, (long long)groups * N, K, K, 128))) return e;
+    return launch_cfg<128, false, 6, false, true>(ma, mb, p, dim3((N + 127) / 128, max_tiles, 1), st, nullptr, 1, &grp);
 }
 
 // Weights as rows, for M <= 256 tokens in tiles of up to 128 (the tiles of one weight tile are neighbours in the grid,

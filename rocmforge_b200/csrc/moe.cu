@@ -90,7 +90,34 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     }
 }
 
+// out[r, :] = x[perm[r] / top, :]: the activations in the sorted order, for a grouped product that reads whole tiles
+// of rows (elem_bytes per element; rows are copied 16 bytes at a time where they are aligned for it)
+__global__ void moe_gather_kernel(const uint8_t* __restrict__ x, long long x_stride_bytes, const int* __restrict__ perm,
+                                  int top, uint8_t* __restrict__ out, int row_bytes, int vec) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const uint8_t* src = x + (size_t)(perm[r] / top) * x_stride_bytes;
+    uint8_t* dst = out + (size_t)r * row_bytes;
+    if (vec) {
+        for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 extern "C" {
+int rf_moe_gather(const void* x, long long x_stride_bytes, const int* perm, int top, void* out, int row_bytes, int n,
+                  cudaStream_t st) {
+    if (n <= 0 || row_bytes <= 0) return 0;
+    const int vec = row_bytes % 16 == 0 && x_stride_bytes % 16 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+                    !(reinterpret_cast<uintptr_t>(out) & 15);
+    rf_launch(moe_gather_kernel, dim3(n), dim3(128), 0, st, reinterpret_cast<const uint8_t*>(x), x_stride_bytes, perm, top,
+              reinterpret_cast<uint8_t*>(out), row_bytes, vec);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
 int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > E) return RF_ERR_UNSUPPORTED;

@@ -47,6 +47,12 @@ struct TcParams {
 // measured on the 0.5B shape, a decode step of 1.14 ms became 1.45 ms; up to 384 bytes nothing changes, from 400 on
 // the time is lost.)
 struct TcNoNorm {};
+// The table of a grouped product (kernel variant GROUPED): tiles[0] row tiles, then (group, first row, end row) each;
+// group g uses rows g * group_n .. of the stacked weights.
+struct TcGroup {
+    const int* tiles;
+    int group_n;
+};
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -25,6 +25,10 @@ from .. import kernels
 from .batch import StepRequest
 
 
+PAGE = 64          # positions a cache page holds
+MAX_LIVE = 256     # requests that may be live at once in a replay
+
+
 class TraceError(ValueError):
     pass
 
@@ -84,7 +88,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder the logits are written to")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (room for each request's last, partly filled "
+                         "page is added)")
     args = ap.parse_args(argv)
 
     from .model import Model
@@ -93,6 +98,7 @@ def main(argv=None) -> int:
         return 2
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     model = Model.from_folder(args.model, dtype=dtype, device="cuda:0")
-    cache = model.new_cache(max_tokens=args.max_tokens)
+    # a request holds whole pages: up to 63 positions more than its tokens, for up to MAX_LIVE requests at a time
+    cache = model.new_cache(max_tokens=args.max_tokens + PAGE * MAX_LIVE, max_slots=MAX_LIVE)
     replay(model, cache, sys.stdin, args.out)
     return 0

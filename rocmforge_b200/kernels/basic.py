@@ -460,10 +460,14 @@ def attention_prefill_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int)
 
 def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                          q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
-                         window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+                         window: int | None, out: torch.Tensor | None = None, *, softcap: float | None = None,
+                         slopes: torch.Tensor | None = None) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products as tcgen05.mma (accumulators in tensor
-    memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles."""
-    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table)
+    memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles.  ``softcap`` and ``slopes`` as in
+    ``attention_generic``."""
+    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table, slopes)
+    need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
+         "attention_prefill_tc: slopes must be float32 [heads]")
     T = q.shape[0]
     need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim,
          "attention_prefill_tc: q must be bfloat16 [T, >= heads*head_dim]")
@@ -477,13 +481,13 @@ def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     if out is None:
         out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     from .tensor_core import status_word
-    f = _f("attention_prefill_tc", "rf_attention_prefill_tc", c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    f = _f("attention_prefill_tc", "rf_attention_prefill_tc_ext", c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
            c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-           c_int, c_void_p, c_void_p)
+           c_int, c_float, c_void_p, c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), T, ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
             q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
-            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
-            ptr(status_word(q.device)), stream()),
+            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0),
+            ptr(slopes), ptr(status_word(q.device)), stream()),
           f"attention_prefill_tc (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
 
@@ -656,6 +660,18 @@ def retention_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, e
 # ---------------------------------------------------------------- routing of experts (csrc/moe.cu)
 
 MOE_TILE_SMALL, MOE_TILE_LARGE = 16, 64
+MOE_TILE_TC = 128          # rows of a tile of the grouped tensor-core product
+
+
+def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int) -> torch.Tensor:
+    """out[r] = x[perm[r] // top]: the tokens' activations in the order the sort left their (token, choice) pairs in."""
+    need_cuda(x, perm)
+    need(x.dim() == 2 and x.stride(1) == 1 and perm.dtype == torch.int32, "moe_gather: x [T, K] and an int32 permutation")
+    n, K = perm.numel(), x.shape[1]
+    out = torch.empty((n, K), dtype=x.dtype, device=x.device)
+    f = _f("moe", "rf_moe_gather", c_void_p, c_ll, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
+    check(f(ptr(x), x.stride(0) * x.element_size(), ptr(perm), top, ptr(out), K * x.element_size(), n, stream()), "moe_gather")
+    return out
 
 
 def moe_route(logits: torch.Tensor, top: int):

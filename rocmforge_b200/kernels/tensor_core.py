@@ -165,6 +165,33 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
+def grouped_supported(N: int, K: int, mode: int) -> bool:
+    """Whether the grouped tensor-core product takes weights [groups, N, K] in this mode."""
+    return mode in (STORE, F32, SWIGLU) and supported(128, N, K, mode)
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, *, mode: int = STORE) -> torch.Tensor:
+    """One launch for many weight matrices: ``x`` [n, K] holds rows sorted by group, ``w`` [groups, N, K] the stacked
+    weights, ``tiles`` the table that ``kernels.moe_sort`` built for row tiles of 128.  STORE -> bf16 [n, N];
+    F32 -> f32 [n, N]; SWIGLU -> bf16 [n, N/2] from row-interleaved gate/up weights."""
+    need_cuda(x, w, tiles)
+    need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 3 and x.stride(1) == 1
+         and w.is_contiguous() and x.shape[1] == w.shape[2], "grouped gemm: x [n, K] and w [groups, N, K] in bfloat16")
+    need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0,
+         "grouped gemm: operands must be 16-byte aligned")
+    need(tiles.dtype == torch.int32 and tiles.numel() >= 1 + 3 * max_tiles, "grouped gemm: tile table too small")
+    n, K = x.shape
+    G, N, _ = w.shape
+    need(grouped_supported(N, K, mode), f"grouped gemm: {N}x{K} in mode {mode} is not supported")
+    cols = N // 2 if mode == SWIGLU else N
+    out = torch.empty((n, cols), dtype=torch.float32 if mode == F32 else torch.bfloat16, device=x.device)
+    f = _f("rf_gemm_tc_grouped", c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+           c_int, c_void_p, c_void_p)
+    check(f(ptr(x), x.stride(0), n, ptr(w), G, N, K, ptr(out), out.stride(0), mode, ptr(tiles), max_tiles,
+            ptr(status_word(x.device)), stream()), f"gemm_tc_grouped ({G} x {N}x{K})")
+    return out
+
+
 def split_k_for(N: int, K: int, sm_count: Optional[int] = None, tokens: Optional[int] = None) -> int:
     """K splits of a skinny product, from N and K (never from the batch's content), so that about two CTAs per SM stream
     the weight and every split keeps at least 4 blocks of 64.  ``tokens``: a step of at most 16 tokens fits three CTAs on an

@@ -31,8 +31,10 @@ class GQAAttention(Mixer):
     ``qk_norm_eps`` (every query and key head divided by its root mean square, x / sqrt(mean(x^2) + eps), no weight,
     before the rotation), ``softcap`` (score <- softcap * tanh(score / softcap) after scaling), ``distance_slopes``
     (one slope per head: after the cap a score is lowered by slope * (query position - key position)), and ``names``
-    (the tensors' names below the part's prefix, keys q, k, v, o).  A mixer with any of the first four takes the
-    generic attention kernel, which knows them all.
+    (the tensors' names below the part's prefix, keys q, k, v, o).  Normed heads and values of another size go into the
+    cache through the per-head writer; a cap and slopes are known to the generic attention and to the tcgen05 prompt
+    attention (heads of 64 or 128 with values of the same size), so prompts of such a mixer run on the tensor cores and
+    its single-token steps on the generic kernel.
     """
 
     accepts_scaled_rows = True
@@ -60,9 +62,10 @@ class GQAAttention(Mixer):
         self.kv_size = n_kv_heads * head_dim
         self.v_size = n_kv_heads * self.v_head_dim
         self.o_in = n_heads * self.v_head_dim
-        # what the tuned kernels do not know: these mixers use the generic attention and the per-head cache writer
-        self.plain_only = (self.v_head_dim != head_dim or self.qk_norm_eps is not None or self.softcap is not None
-                           or self.distance_slopes is not None)
+        # normed heads and values of another size: the per-head cache writer; a cap or slopes: no mma.sync kernel knows them
+        self.plain_projection = self.v_head_dim != head_dim or self.qk_norm_eps is not None
+        self.shaped_scores = self.softcap is not None or self.distance_slopes is not None
+        self.plain_only = self.plain_projection or self.shaped_scores
         if self.plain_only and (qkv_bias or o_bias):
             raise ValueError("gqa_attention: biases do not go with normed heads, a score cap, distance slopes or another value size")
         self.qkv: Optional[Linear] = None
@@ -113,7 +116,7 @@ class GQAAttention(Mixer):
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
 
     def step_table_names(self):
-        return () if self.plain_only else tuple(self.TILE_ROWS)
+        return () if self.v_head_dim != self.head_dim else tuple(self.TILE_ROWS)
 
     def step_table(self, name, batch):
         """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
@@ -169,7 +172,7 @@ class GQAAttention(Mixer):
         y, row_ss = ctx.unpack_rows(y, w, tc.PARTIAL)
         rot = dict((self.position.rotation() if self.position is not None else None) or dict(inv_freq=None, rot_dim=0))
         inv_freq = rot.pop("inv_freq")
-        if self.plain_only:
+        if self.plain_projection:
             return self._project_plain(ctx, y, view, rot, inv_freq)
         rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot,
                     block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
@@ -198,10 +201,11 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         tiles64, tiles128 = ctx.tables.get("attention_tiles64"), ctx.tables.get("attention_tiles128")
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
-        if self.plain_only:
+        shaped = dict(softcap=self.softcap, slopes=self.slopes_dev)
+        if self.v_head_dim != hd or (self.shaped_scores and (ctx.is_decode or ctx.compute_dtype != torch.bfloat16)):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, view.window,
-                                             v_head_dim=self.v_head_dim, softcap=self.softcap, slopes=self.slopes_dev)
+                                             v_head_dim=self.v_head_dim, **shaped)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
             if ctx.options.clustered_decode:
@@ -233,7 +237,10 @@ class GQAAttention(Mixer):
                 and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
             return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles128,
                                                 ctx.seq_slot, ctx.seq_start, ctx.seq_nnew, ctx.cu_q,
-                                                view.block_table, self.scale, view.window)
+                                                view.block_table, self.scale, view.window, **shaped)
+        if self.shaped_scores:
+            return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
+                                             ctx.seq_slot, view.block_table, self.scale, view.window, **shaped)
         if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and tiles64 is not None and tiles64.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
                 and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):

@@ -39,9 +39,10 @@ class RoutedExperts(FeedForward):
         return f"{self.expert_prefix}{e}.{self.names[which]}"
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        s = {self.names["router"]: ParamSpec((self.n_experts, self.hidden))}
+        # random-weights mode: router logits a few units apart, so that a choice rarely hangs on the last bits
+        s = {self.names["router"]: ParamSpec((self.n_experts, self.hidden), std=0.5)}
         if self.router_bias:
-            s[self.names["router_bias"]] = ParamSpec((self.n_experts,), kind="vector", init="zeros")
+            s[self.names["router_bias"]] = ParamSpec((self.n_experts,), kind="vector", init="normal", std=0.5)
         for e in range(self.n_experts):
             s[self._expert(e, "gate")] = ParamSpec((self.intermediate, self.hidden))
             s[self._expert(e, "up")] = ParamSpec((self.intermediate, self.hidden))
@@ -58,7 +59,7 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([params[self._expert(e, "down")] for e in range(E)]).contiguous()      # [E, H, F]
 
     def cuda_modules(self, compute_dtype):
-        return ["elementwise", "gemm_simt", "moe"]
+        return ["elementwise", "gemm_simt", "moe"] + (["gemm_tcgen05"] if compute_dtype == torch.bfloat16 else [])
 
     def output(self, ctx, y):
         if isinstance(y, ScaledRows):
@@ -66,9 +67,19 @@ class RoutedExperts(FeedForward):
         T = y.shape[0]
         z = kernels.gemm_simt(y, self.router_w, self.router_b, out_f32=True)                 # 32-bit sums, any shape
         idx, w = kernels.moe_route(z, self.top)
-        rows = kernels.MOE_TILE_SMALL if T * self.top <= 16 * self.n_experts else kernels.MOE_TILE_LARGE
-        perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
         n = T * self.top
+        tc = kernels.tensor_core
+        if (ctx.compute_dtype == torch.bfloat16 and ctx.options.tensor_core_gemm
+                and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.SWIGLU)
+                and tc.grouped_supported(self.hidden, self.intermediate, tc.F32)):
+            # tensor cores: the activations once in sorted order, then tiles of 128 sorted rows against their expert's
+            # matrices; the gate's silu and the product with up happen in the first product's epilogue
+            perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, kernels.MOE_TILE_TC)
+            a = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.SWIGLU)
+            d = tc.gemm_tc_grouped(a, self.down, tiles, max_tiles, mode=tc.F32)
+            return kernels.moe_combine(d, inv, w)
+        rows = kernels.MOE_TILE_SMALL if n <= 16 * self.n_experts else kernels.MOE_TILE_LARGE
+        perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
         gu = kernels.gemm_simt_grouped(y, self.gate_up, tiles, max_tiles, rows, n, row_map=perm, row_div=self.top)
         a = kernels.swiglu(gu)                                                               # [n, F], sorted rows
         d = kernels.gemm_simt_grouped(a, self.down, tiles, max_tiles, rows, n, out_f32=True)

@@ -26,14 +26,17 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def folders(tmp_path_factory):
     """Factory: (config name, dtype) -> model folder with random weights, made once per session."""
-    from helpers import CONFIGS, write_tiny
+    from helpers import CONFIGS, RIFIZEN_CONFIGS, write_rifizen, write_tiny
     made = {}
 
     def get(name: str, dtype: str = "float32") -> str:
         key = (name, dtype)
         if key not in made:
             d = tmp_path_factory.mktemp(f"model_{name}_{dtype}")
-            write_tiny(CONFIGS[name], str(d), dtype)
+            if name in RIFIZEN_CONFIGS:
+                write_rifizen(RIFIZEN_CONFIGS[name], str(d), dtype)
+            else:
+                write_tiny(CONFIGS[name], str(d), dtype)
             made[key] = str(d)
         return made[key]
     return get

@@ -85,7 +85,8 @@ class TraceRun:
 
     def __init__(self, folder: str, dtype: str, out_dir: str, max_tokens: int, env=None):
         self.out_dir = out_dir
-        self.vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
+        cfg = json.load(open(os.path.join(folder, "config.json")))
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
         self.proc = subprocess.Popen(
             [os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", out_dir,
              "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
@@ -109,3 +110,65 @@ class TraceRun:
     def close(self) -> int:
         self.proc.stdin.close()
         return self.proc.wait(timeout=120)
+
+
+# --------------------------------------------------------------------------- Rifizen
+
+def rifizen_layer(*, heads, kv_heads, dim, vdim, window, scale, softcap, r_heads, r_dim, r_vdim, decay, rot_dims,
+                  rot_base, mlp):
+    return {"type": "parallel",
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": window},
+                               "scale": scale, "softcap": softcap},
+                      "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": list(decay),
+                                "rot": {"dims": rot_dims, "base": rot_base}}},
+            "mlp": mlp}
+
+
+def _dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def _moe(ff, experts, top):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+# Sizes that differ from each other in every respect: values of another size than keys, value columns that do not
+# fill a group of eight, a partly rotated head, decays of exactly 1 and far below, a layer without feed-forward, a
+# loop that starts at the first layer / in the middle / is absent, one expert per token and several, windows below
+# and above a page, as many kv heads as heads and one for all.
+RIFIZEN_A = dict(seed=11, architecture="Rifizen", vocab=96, width=64, norm={"eps": 1e-5},
+                 loop={"start": 0, "stop": 2, "times": 2},
+                 layers=[rifizen_layer(heads=4, kv_heads=2, dim=16, vdim=24, window=7, scale=0.3, softcap=5.0, r_heads=2,
+                                       r_dim=24, r_vdim=12, decay=[0.9, 1.0], rot_dims=8, rot_base=100.0, mlp=_dense(40)),
+                         rifizen_layer(heads=4, kv_heads=2, dim=16, vdim=24, window=3, scale=0.3, softcap=5.0, r_heads=2,
+                                       r_dim=24, r_vdim=12, decay=[0.5, 0.99], rot_dims=8, rot_base=100.0, mlp=_moe(20, 5, 2)),
+                         rifizen_layer(heads=2, kv_heads=1, dim=8, vdim=8, window=1, scale=1.0, softcap=2.0, r_heads=1,
+                                       r_dim=40, r_vdim=20, decay=[0.97], rot_dims=40, rot_base=50.0, mlp=None)])
+RIFIZEN_B = dict(seed=12, architecture="Rifizen", vocab=200, width=128, norm={"eps": 1e-6},
+                 layers=[rifizen_layer(heads=3, kv_heads=3, dim=40, vdim=40, window=70, scale=0.05, softcap=50.0, r_heads=3,
+                                       r_dim=64, r_vdim=32, decay=[0.8, 0.999, 0.99], rot_dims=32, rot_base=1e4,
+                                       mlp=_moe(48, 8, 1)),
+                         rifizen_layer(heads=9, kv_heads=1, dim=20, vdim=12, window=130, scale=0.2, softcap=8.0, r_heads=2,
+                                       r_dim=96, r_vdim=64, decay=[0.95, 0.9999], rot_dims=96, rot_base=1e6,
+                                       mlp=_dense(100))])
+RIFIZEN_C = dict(seed=13, architecture="Rifizen", vocab=300, width=256, norm={"eps": 1e-6},
+                 loop={"start": 1, "stop": 2, "times": 3},
+                 layers=[rifizen_layer(heads=8, kv_heads=2, dim=64, vdim=64, window=100, scale=0.125, softcap=20.0, r_heads=4,
+                                       r_dim=64, r_vdim=64, decay=[0.9, 0.99, 0.999, 0.9999], rot_dims=64, rot_base=1e5,
+                                       mlp=_moe(64, 4, 2)),
+                         rifizen_layer(heads=4, kv_heads=4, dim=32, vdim=48, window=33, scale=0.18, softcap=30.0, r_heads=8,
+                                       r_dim=32, r_vdim=16, decay=[0.5, 0.75, 0.9, 0.95, 0.97, 0.98, 0.99, 0.995],
+                                       rot_dims=16, rot_base=1e4, mlp=_dense(320)),
+                         rifizen_layer(heads=4, kv_heads=1, dim=128, vdim=128, window=64, scale=0.09, softcap=15.0, r_heads=2,
+                                       r_dim=128, r_vdim=128, decay=[0.98, 0.999], rot_dims=64, rot_base=1e4,
+                                       mlp=_moe(96, 6, 3))])
+RIFIZEN_CONFIGS = {"RA": RIFIZEN_A, "RB": RIFIZEN_B, "RC": RIFIZEN_C}
+
+
+def write_rifizen(cfg: dict, folder: str, dtype: str = "float32") -> None:
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import architecture_for
+    arch = architecture_for("Rifizen")
+    c = arch.config_cls.from_dict(config_dict(cfg))
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    rf.write_model_folder(folder, c.to_dict(), arch.build(c).param_specs(), cfg["seed"], dt)
