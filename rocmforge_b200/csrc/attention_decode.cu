@@ -332,7 +332,8 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
                               const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                               int out_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                               const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
-                              int nh, int nkv, float scale, int window, int splits, int* __restrict__ status) {
+                              int nh, int nkv, float scale, int window, int splits, int* __restrict__ status,
+                              float softcap, const float* __restrict__ slopes) {
     constexpr int HD = EPL * 32;
     constexpr int NT = WARPS * 32;
     constexpr int HALVES = HD / 64;                             // 128-byte column blocks of a row
@@ -359,6 +360,13 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
     const int rank = splits > 1 ? (int)dcl_cluster_rank() : 0;
     const int pos = tok_pos[b];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    // designs that cap their scores (softcap * tanh(score / softcap)) and lower them by slope * distance afterwards
+    const bool shaped = softcap > 0.f || slopes != nullptr;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    float slope2[2] = {0.f, 0.f};                       // of this lane's two heads
+    if (slopes != nullptr)
+        for (int h = 0; h < 2; ++h)
+            if (tig * 2 + h < G) slope2[h] = slopes[kvh * G + tig * 2 + h];
     const int p_lo = lo / RF_PAGE, p_hi = pos / RF_PAGE;
     const int n_my = (p_hi - p_lo - rank) >= 0 ? (p_hi - p_lo - rank) / splits + 1 : 0;     // pages of this CTA
     const int n_units = n_my * UPP;
@@ -476,7 +484,12 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kk = kb * 16 + gid + (e >> 1) * 8;
-                sc[kb][e] = (kk >= k_begin && kk <= k_last) ? sc[kb][e] * scale : -INFINITY;
+                float v = sc[kb][e] * scale;
+                if (shaped) {
+                    if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
+                    v -= slope2[e & 1] * (float)(pos - (key0 + kk));
+                }
+                sc[kb][e] = (kk >= k_begin && kk <= k_last) ? v : -INFINITY;
                 mx[e & 1] = fmaxf(mx[e & 1], sc[kb][e]);
             }
         float corr[2], psum[2] = {0.f, 0.f};
@@ -670,7 +683,7 @@ template <int EPL, int ROWS, int WARPS>
 static int launch_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
                         const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, float scale,
-                        int window, int B, int splits, int* status, cudaStream_t st) {
+                        int window, int B, int splits, int* status, float softcap, const float* slopes, cudaStream_t st) {
     constexpr int HD = EPL * 32;
     const size_t smem = (size_t)WARPS * 2 * ROWS * HD * 2 +
                         (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 16 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
@@ -711,7 +724,7 @@ static int launch_warps(const void* q, int q_stride, void* out, int out_stride, 
         return me;
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_warps_kernel<EPL, ROWS, WARPS>, mk, mv,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride, tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status);
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status, softcap, slopes);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -760,10 +773,13 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
 }
 
 // A warp per tile of keys, `warps` (4 or 8) warps per CTA.
-int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                              const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
-                              const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
-                              float scale, int window, int B, int splits, int warps, int* status, cudaStream_t st) {
+// softcap > 0: scores become softcap * tanh(score / softcap); slopes (float [nh] or null): after the cap a score is
+// lowered by slopes[head] * (query position - key position).
+int rf_attention_decode_warps_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                  const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                                  const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
+                                  float scale, int window, int B, int splits, int warps, float softcap, const float* slopes,
+                                  int* status, cudaStream_t st) {
     if (B <= 0) return 0;
     if (!rf_attention_decode_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
     if (nkv > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
@@ -771,12 +787,21 @@ int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_st
     if (warps != 4 && warps != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
 #define GOW(EPL, ROWS, WARPS) return launch_warps<EPL, ROWS, WARPS>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, \
-                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, st)
+                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, softcap, slopes, st)
     if (hd == 64) { if (warps == 8) GOW(2, 32, 8); GOW(2, 32, 4); }
     if (hd == 128) { if (warps == 8) GOW(4, 32, 8); GOW(4, 32, 4); }
     if (warps == 8) GOW(8, 16, 8);
     GOW(8, 16, 4);
 #undef GOW
+}
+
+int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                              const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                              const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
+                              float scale, int window, int B, int splits, int warps, int* status, cudaStream_t st) {
+    return rf_attention_decode_warps_ext(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, tok_pos, seq_slot,
+                                         block_table, max_pages, nh, nkv, hd, scale, window, B, splits, warps, 0.f, nullptr,
+                                         status, st);
 }
 
 int rf_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -489,15 +489,17 @@ __global__ void add_row_kernel(float* __restrict__ h, const T* __restrict__ vec,
 //   m = (rms(a0) * w0 + rms(a1) * w1) / 2             (two branches side by side, each normed with its own weight)
 //   h += rms(m) * w_post (+ extra)                    (extra: a row vector that the schedule adds before the next layer)
 //   y_next = rms(h) * w_next in the compute dtype     (the norm that reads the stream next, if the caller knows it)
-// with rms(x) = x / sqrt(mean(x^2) + eps).  A block per row; the row stays in shared memory between the passes.
+// with rms(x) = x / sqrt(mean(x^2) + eps).  A branch comes as n0 (n1) partial sums [n][rows][H] of a K-split product,
+// added here in index order.  A block per row; the rows stay in shared memory between the passes.
 template <typename T>
 __global__ void __launch_bounds__(256)
-branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, const void* __restrict__ w0,
-                       const float* __restrict__ a1, const void* __restrict__ w1, const void* __restrict__ w_post,
-                       const void* __restrict__ extra, const void* __restrict__ w_next, T* __restrict__ y_next,
-                       int w_is_f32, float eps, int H) {
-    extern __shared__ float row[];                  // [H] + 34 for the sums
-    float* red = row + H;
+branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int n0, const void* __restrict__ w0,
+                       const float* __restrict__ a1, int n1, size_t part_stride, const void* __restrict__ w1,
+                       const void* __restrict__ w_post, const void* __restrict__ extra, const void* __restrict__ w_next,
+                       T* __restrict__ y_next, int w_is_f32, float eps, int H) {
+    extern __shared__ float row[];                  // [H], a second [H] for the other branch, 34 for the sums
+    float* other = row + H;
+    float* red = other + H;
     pdl_trigger();
     const size_t base = (size_t)blockIdx.x * H;
     const float invH = 1.f / (float)H;
@@ -505,15 +507,22 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, cons
     if (a1 != nullptr) {
         float s0 = 0.f, s1 = 0.f;
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
-            const float x = a0[base + c], z = a1[base + c];
+            float x = 0.f, z = 0.f;
+            for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
+            for (int s = 0; s < n1; ++s) z += a1[(size_t)s * part_stride + base + c];
+            row[c] = x; other[c] = z;
             s0 += x * x; s1 += z * z;
         }
         const float r0 = rsqrtf(block_sum(s0, red) * invH + eps);
         const float r1 = rsqrtf(block_sum(s1, red) * invH + eps);
         for (int c = threadIdx.x; c < H; c += blockDim.x)
-            row[c] = 0.5f * (a0[base + c] * r0 * load_vec(w0, w_is_f32, c) + a1[base + c] * r1 * load_vec(w1, w_is_f32, c));
+            row[c] = 0.5f * (row[c] * r0 * load_vec(w0, w_is_f32, c) + other[c] * r1 * load_vec(w1, w_is_f32, c));
     } else {
-        for (int c = threadIdx.x; c < H; c += blockDim.x) row[c] = a0[base + c];
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float x = 0.f;
+            for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
+            row[c] = x;
+        }
     }
     float sm = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) sm += row[c] * row[c];      // a thread reads what it wrote
@@ -731,11 +740,12 @@ static int launch_add_row(float* h, const void* vec, int T_, int H, cudaStream_t
 }
 
 template <typename T>
-static int launch_branch_norm_add(float* h, const float* a0, const void* w0, const float* a1, const void* w1,
-                                  const void* w_post, const void* extra, const void* w_next, void* y_next,
+static int launch_branch_norm_add(float* h, const float* a0, int n0, const void* w0, const float* a1, int n1,
+                                  const void* w1, const void* w_post, const void* extra, const void* w_next, void* y_next,
                                   int w_is_f32, float eps, int rows, int H, cudaStream_t st) {
     if (rows <= 0) return 0;
-    const size_t smem = (size_t)(H + 34) * sizeof(float);
+    if (n0 < 1 || (a1 != nullptr && n1 < 1)) return RF_ERR_BAD_ARG;
+    const size_t smem = (size_t)(2 * H + 34) * sizeof(float);
     if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
@@ -743,8 +753,8 @@ static int launch_branch_norm_add(float* h, const float* a0, const void* w0, con
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    rf_launch(branch_norm_add_kernel<T>, dim3(rows), dim3(256), smem, st, h, a0, w0, a1, w1, w_post, extra, w_next,
-              reinterpret_cast<T*>(y_next), w_is_f32, eps, H);
+    rf_launch(branch_norm_add_kernel<T>, dim3(rows), dim3(256), smem, st, h, a0, n0, w0, a1, n1, (size_t)rows * H, w1, w_post,
+              extra, w_next, reinterpret_cast<T*>(y_next), w_is_f32, eps, H);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -808,12 +818,13 @@ int rf_add_row(int dtype, float* h, const void* vec, int T_, int H, cudaStream_t
     return dtype == 0 ? launch_add_row<float>(h, vec, T_, H, st) : launch_add_row<__nv_bfloat16>(h, vec, T_, H, st);
 }
 // a1 / w1 null: one branch, taken as it is; extra, w_next / y_next null: left out.  All weight vectors share w_is_f32.
-int rf_branch_norm_add(int dtype, float* h, const float* a0, const void* w0, const float* a1, const void* w1,
+// a0 / a1 are stacks of n0 / n1 partial sums, each [rows][H] (1: the branch itself).
+int rf_branch_norm_add(int dtype, float* h, const float* a0, int n0, const void* w0, const float* a1, int n1, const void* w1,
                        const void* w_post, const void* extra, const void* w_next, void* y_next, int w_is_f32, float eps,
                        int rows, int H, cudaStream_t st) {
     return dtype == 0
-        ? launch_branch_norm_add<float>(h, a0, w0, a1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st)
-        : launch_branch_norm_add<__nv_bfloat16>(h, a0, w0, a1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st);
+        ? launch_branch_norm_add<float>(h, a0, n0, w0, a1, n1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st)
+        : launch_branch_norm_add<__nv_bfloat16>(h, a0, n0, w0, a1, n1, w1, w_post, extra, w_next, y_next, w_is_f32, eps, rows, H, st);
 }
 int rf_head_norm_kv_write(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride, void* q_out,
                           int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq, const int* tok_seq,

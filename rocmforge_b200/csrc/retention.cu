@@ -133,6 +133,227 @@ __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __re
     }
 }
 
+// ---------------------------------------------------------------- prompts: the recurrence in chunks of 64 tokens
+// The same sums in another order, so that a prompt's chunks run side by side instead of token after token.  With
+// positions t, s inside a chunk of cnt tokens, S0 the state before the chunk and d the head's decay:
+//   pass 1 (chunks side by side)   L = sum_s d^(cnt-1-s) k_s v_s^T                              [dim, vdim]
+//   pass 2 (chunk after chunk, element by element)   S0 of every chunk; the state after the last one
+//                                   S0(next) = d^cnt S0 + L      (L's place in memory becomes S0's)
+//   pass 3 (chunks side by side)   o_t = sum_(s<=t) d^(t-s) (q_t . k_s) v_s + d^(t+1) S0^T q_t
+// All in 32-bit on the CUDA cores (the scores of this mixer are not rounded to 16 bits).  The chunk table is built on
+// the host with the step: first[B+1] (index of each sequence's first chunk), then (sequence, first row) per chunk.
+#define RC 64                 // tokens of a chunk
+#define RC_LD 68              // row stride of the transposed tiles: rows stay 16-byte aligned
+#define RV 64                 // value columns of a block
+
+// grid (chunk, head, ceil(vdim / RV)); 256 threads: thread (ty, tx) owns rows ty + 16 r and columns 4 tx .. 4 tx + 3
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_chunk_state_kernel(const float* __restrict__ k, const T* __restrict__ v, int v_stride, float* __restrict__ LS,
+                             const float* __restrict__ decay, const int* __restrict__ table, const int* __restrict__ cu_q,
+                             int B, int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float sh[];
+    float* ks = sh;                                   // [RC][dim], already times d^(cnt-1-s)
+    float* vs = ks + RC * dim;                        // [RC][RV]
+    pdl_trigger();
+    const int c = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * RV;
+    const int b = table[B + 1 + 2 * c], q0 = table[B + 2 + 2 * c];
+    const int row0 = cu_q[b] + q0, cnt = min(RC, cu_q[b + 1] - row0);
+    const float d = decay[h];
+    const int width = heads * dim;
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < cnt * dim; idx += 256) {
+        const int s = idx / dim, i = idx - s * dim;
+        ks[idx] = k[(size_t)(row0 + s) * width + h * dim + i] * powf(d, (float)(cnt - 1 - s));
+    }
+    for (int idx = threadIdx.x; idx < cnt * RV; idx += 256) {
+        const int s = idx / RV, j = idx - s * RV;
+        vs[idx] = (j0 + j < vdim) ? Cvt<T>::to_f32(v[(size_t)(row0 + s) * v_stride + h * vdim + j0 + j]) : 0.f;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[16][4];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) { acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f; }
+    for (int s = 0; s < cnt; ++s) {
+        const float4 vv = *reinterpret_cast<const float4*>(&vs[s * RV + 4 * tx]);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int i = ty + 16 * r;
+            if (i < dim) {
+                const float kk = ks[s * dim + i];
+                acc[r][0] = fmaf(kk, vv.x, acc[r][0]); acc[r][1] = fmaf(kk, vv.y, acc[r][1]);
+                acc[r][2] = fmaf(kk, vv.z, acc[r][2]); acc[r][3] = fmaf(kk, vv.w, acc[r][3]);
+            }
+        }
+    }
+    float* out = LS + (((size_t)c * heads + h) * dim) * vdim;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int i = ty + 16 * r;
+        if (i < dim)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j0 + 4 * tx + u < vdim) out[(size_t)i * vdim + j0 + 4 * tx + u] = acc[r][u];
+    }
+}
+
+// grid (sequence, head, blocks over dim * vdim); a thread owns one element of the state through all chunks
+__global__ void retention_chunk_carry_kernel(float* __restrict__ LS, float* __restrict__ state, const float* __restrict__ decay,
+                                             const int* __restrict__ table, const int* __restrict__ cu_q,
+                                             const int* __restrict__ seq_slot, int heads, int dim, int vdim) {
+    pdl_trigger();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= dim * vdim) return;
+    const int c0 = table[b], c1 = table[b + 1];
+    const int n_new = cu_q[b + 1] - cu_q[b];
+    const float d = decay[h];
+    const float d_full = powf(d, (float)RC);
+    float* S = state + (((size_t)seq_slot[b] * heads + h) * dim) * vdim + e;
+    pdl_wait();
+    float s = *S;
+    for (int c = c0; c < c1; ++c) {
+        float* p = LS + (((size_t)c * heads + h) * dim) * vdim + e;
+        const float l = *p;
+        *p = s;                                          // the state before chunk c
+        const int cnt = min(RC, n_new - (c - c0) * RC);
+        s = fmaf(cnt == RC ? d_full : powf(d, (float)cnt), s, l);
+    }
+    *S = s;
+}
+
+// grid (chunk, head, ceil(vdim / RV)); 256 threads as a 16 x 16 grid of 4 x 4 tiles
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_chunk_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const T* __restrict__ v, int v_stride,
+                           const float* __restrict__ LS, const float* __restrict__ decay, float* __restrict__ o,
+                           const int* __restrict__ table, const int* __restrict__ cu_q, int B, int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float sh[];
+    float* qt = sh;                                   // [dim][RC_LD]: q transposed
+    float* kt = qt + dim * RC_LD;                     // [dim][RC_LD]: k transposed; later the state S0 as [dim][RV]
+    float* vs = kt + dim * RC_LD;                     // [RC][RV]
+    float* at = vs + RC * RV;                         // [RC (s)][RC_LD (t)]: the decayed scores, transposed
+    float* pw = at + RC * RC_LD;                      // d^0 .. d^RC
+    pdl_trigger();
+    const int c = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * RV;
+    const int b = table[B + 1 + 2 * c], q0 = table[B + 2 + 2 * c];
+    const int row0 = cu_q[b] + q0, cnt = min(RC, cu_q[b + 1] - row0);
+    const float d = decay[h];
+    const int width = heads * dim;
+    if (threadIdx.x <= RC) pw[threadIdx.x] = powf(d, (float)threadIdx.x);
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < RC * dim; idx += 256) {
+        const int s = idx / dim, i = idx - s * dim;
+        const bool in = s < cnt;
+        qt[i * RC_LD + s] = in ? q[(size_t)(row0 + s) * width + h * dim + i] : 0.f;
+        kt[i * RC_LD + s] = in ? k[(size_t)(row0 + s) * width + h * dim + i] : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < RC * RV; idx += 256) {
+        const int s = idx / RV, j = idx - s * RV;
+        vs[idx] = (s < cnt && j0 + j < vdim) ? Cvt<T>::to_f32(v[(size_t)(row0 + s) * v_stride + h * vdim + j0 + j]) : 0.f;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;        // rows (t) 4 ty .., columns 4 tx ..
+    {
+        // scores: a[t][s] = (q_t . k_s) d^(t-s) for s <= t
+        float a[4][4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) { a[x][0] = a[x][1] = a[x][2] = a[x][3] = 0.f; }
+        if (tx <= ty) {                                  // tiles above the diagonal are zero
+            for (int i = 0; i < dim; ++i) {
+                const float4 qq = *reinterpret_cast<const float4*>(&qt[i * RC_LD + 4 * ty]);
+                const float4 kk = *reinterpret_cast<const float4*>(&kt[i * RC_LD + 4 * tx]);
+                const float qv[4] = {qq.x, qq.y, qq.z, qq.w}, kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+#pragma unroll
+                    for (int y = 0; y < 4; ++y) a[x][y] = fmaf(qv[x], kv[y], a[x][y]);
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+                const int t = 4 * ty + x, s = 4 * tx + y;
+                at[s * RC_LD + t] = (s <= t) ? a[x][y] * pw[t - s] : 0.f;
+            }
+    }
+    __syncthreads();                                     // k is used up: its place takes the state before the chunk
+    const float* S0 = LS + (((size_t)c * heads + h) * dim) * vdim;
+    for (int idx = threadIdx.x; idx < dim * RV; idx += 256) {
+        const int i = idx / RV, j = idx - i * RV;
+        kt[idx] = (j0 + j < vdim) ? S0[(size_t)i * vdim + j0 + j] : 0.f;
+    }
+    __syncthreads();
+    float o1[4][4], o2[4][4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) { o1[x][y] = 0.f; o2[x][y] = 0.f; }
+    const int s_end = min(cnt, 4 * ty + 4);              // later keys have zero scores for these rows
+    for (int s = 0; s < s_end; ++s) {
+        const float4 aa = *reinterpret_cast<const float4*>(&at[s * RC_LD + 4 * ty]);
+        const float4 vv = *reinterpret_cast<const float4*>(&vs[s * RV + 4 * tx]);
+        const float av[4] = {aa.x, aa.y, aa.z, aa.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) o1[x][y] = fmaf(av[x], vw[y], o1[x][y]);
+    }
+    for (int i = 0; i < dim; ++i) {
+        const float4 qq = *reinterpret_cast<const float4*>(&qt[i * RC_LD + 4 * ty]);
+        const float4 ss = *reinterpret_cast<const float4*>(&kt[i * RV + 4 * tx]);
+        const float qv[4] = {qq.x, qq.y, qq.z, qq.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) o2[x][y] = fmaf(qv[x], sv[y], o2[x][y]);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const int t = 4 * ty + x;
+        if (t < cnt)
+#pragma unroll
+            for (int y = 0; y < 4; ++y) {
+                const int j = j0 + 4 * tx + y;
+                if (j < vdim) o[(size_t)(row0 + t) * heads * vdim + h * vdim + j] = fmaf(pw[t + 1], o2[x][y], o1[x][y]);
+            }
+    }
+}
+
+template <typename T>
+static int launch_chunked(const float* q, const float* k, const void* v, int v_stride, float* state, const float* decay,
+                          float* o, float* LS, const int* table, int n_chunks, const int* cu_q, const int* seq_slot, int B,
+                          int heads, int dim, int vdim, cudaStream_t st) {
+    if (B <= 0 || n_chunks <= 0) return 0;
+    if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
+    const int vz = (vdim + RV - 1) / RV;
+    const size_t smem1 = (size_t)(RC * dim + RC * RV) * sizeof(float);
+    const size_t smem3 = (size_t)(2 * dim * RC_LD + RC * RV + RC * RC_LD + RC + 4) * sizeof(float);
+    static size_t set1 = 48 * 1024, set3 = 48 * 1024;
+    if (smem1 > set1) {
+        cudaError_t e = cudaFuncSetAttribute(retention_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+        if (e != cudaSuccess) return (int)e;
+        set1 = smem1;
+    }
+    if (smem3 > set3) {
+        cudaError_t e = cudaFuncSetAttribute(retention_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+        if (e != cudaSuccess) return (int)e;
+        set3 = smem3;
+    }
+    rf_launch(retention_chunk_state_kernel<T>, dim3(n_chunks, heads, vz), dim3(256), smem1, st, k, reinterpret_cast<const T*>(v),
+              v_stride, LS, decay, table, cu_q, B, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    rf_launch(retention_chunk_carry_kernel, dim3(B, heads, (dim * vdim + 255) / 256), dim3(256), 0, st, LS, state, decay, table,
+              cu_q, seq_slot, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    rf_launch(retention_chunk_out_kernel<T>, dim3(n_chunks, heads, vz), dim3(256), smem3, st, q, k, reinterpret_cast<const T*>(v),
+              v_stride, (const float*)LS, decay, o, table, cu_q, B, heads, dim, vdim);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 template <typename T>
 static int launch_prepare(const void* src, int row_stride, int q_col, int k_col, float* qk, int heads, int dim,
                           int rot_dim, const float* inv_freq, const int* tok_pos, float k_scale, int T_, cudaStream_t st) {
@@ -194,6 +415,14 @@ int rf_retention_scan(int dtype, const float* q, const float* k, const void* v, 
                       float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, cudaStream_t st) {
     return dtype == 0 ? launch_scan<float>(q, k, v, v_stride, state, decay, o, cu_q, seq_slot, B, heads, dim, vdim, st)
                       : launch_scan<__nv_bfloat16>(q, k, v, v_stride, state, decay, o, cu_q, seq_slot, B, heads, dim, vdim, st);
+}
+// The recurrence of a prompt step in chunks of 64 tokens (see above).  LS: scratch float [n_chunks, heads, dim, vdim];
+// table: first[B+1], then n_chunks pairs (sequence, first row of the chunk among the sequence's new tokens).
+int rf_retention_chunked(int dtype, const float* q, const float* k, const void* v, int v_stride, float* state, const float* decay,
+                         float* o, float* LS, const int* table, int n_chunks, const int* cu_q, const int* seq_slot, int B,
+                         int heads, int dim, int vdim, cudaStream_t st) {
+    return dtype == 0 ? launch_chunked<float>(q, k, v, v_stride, state, decay, o, LS, table, n_chunks, cu_q, seq_slot, B, heads, dim, vdim, st)
+                      : launch_chunked<__nv_bfloat16>(q, k, v, v_stride, state, decay, o, LS, table, n_chunks, cu_q, seq_slot, B, heads, dim, vdim, st);
 }
 int rf_retention_gate(int dtype, const float* o, const void* gate, int gate_stride, void* out, int heads, int vdim, float eps,
                       int T_, cudaStream_t st) {

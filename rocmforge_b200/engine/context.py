@@ -86,6 +86,24 @@ class StepContext:
             return tc.gemm_tc(x, w, bias, mode=mode)
         return kernels.gemm_simt(x, w, bias, out_f32=out_f32)
 
+    def matmul_f32_parts(self, x, w):
+        """x w^T as float32 [M, N], or for few tokens as the stack [S, M, N] of a K-split product's partial sums (the
+        number of splits follows the weight's shape and the step's token bucket, never the batch's content)."""
+        tc = kernels.tensor_core
+        x, row_ss = self.unpack_rows(x, w, tc.PARTIAL)
+        if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
+            if self.uses_tensor_cores(x, w, tc.PARTIAL):
+                splits = tc.split_k_for(w.shape[0], w.shape[1], tokens=x.shape[0])
+                if splits > 1:
+                    return tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
+            elif row_ss is None:
+                splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
+                if splits > 1:
+                    return kernels.gemm_simt(x, w, splits=splits)
+        if row_ss is not None:
+            x = ScaledRows(x, row_ss[0], row_ss[1], w.shape[1])
+        return self.matmul(x, w, out_f32=True)
+
     def matmul_residual(self, x, w, bias, stream) -> None:
         """stream += x w^T (+ bias), summed in 32-bit: into ``h`` directly, or left pending as the
         32-bit partial sums of a K-split product (the next norm adds them in index order)."""

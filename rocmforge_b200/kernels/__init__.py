@@ -5,6 +5,6 @@ from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, 
                     attention_decode_warps, decode_splits, decode_pages,
                     attention_prefill_tc, attention_prefill_tc_supported, PREFILL_TC_TILE)
 from .basic import (relu2, add_row, branch_norm_add, head_norm_kv_write, gemm_simt_grouped, retention_prepare,
-                    retention_scan, retention_gate, moe_route, moe_sort, moe_combine, moe_gather, MOE_TILE_SMALL, MOE_TILE_LARGE, MOE_TILE_TC)
+                    retention_scan, retention_gate, retention_chunked, RETENTION_CHUNK, moe_route, moe_sort, moe_combine, moe_gather, MOE_TILE_SMALL, MOE_TILE_LARGE, MOE_TILE_TC)
 from ._ffi import launch_count
 from . import tensor_core

@@ -420,7 +420,8 @@ def decode_pages(longest: int, window: int | None) -> int:
 def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                            tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                            splits: int | None = None, warps: int | None = None,
-                           out: torch.Tensor | None = None) -> torch.Tensor:
+                           out: torch.Tensor | None = None, *, softcap: float | None = None,
+                           slopes: torch.Tensor | None = None) -> torch.Tensor:
     """One new token per sequence over the bfloat16 paged cache: a cluster of ``splits`` CTAs per (sequence,
     kv head), every warp on its own tiles of keys; merged through distributed shared memory.  ``warps``
     per CTA: 8 while one CTA per SM is enough for the batch, else 4 (three CTAs fit an SM)."""
@@ -440,12 +441,15 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     from .tensor_core import status_word
-    f = _f("attention_decode", "rf_attention_decode_warps", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    need(slopes is None or (slopes.is_cuda and slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
+         "attention_decode: slopes must be float32 [heads]")
+    f = _f("attention_decode", "rf_attention_decode_warps_ext", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
            c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
-           c_void_p, c_void_p)
+           c_float, c_void_p, c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(tok_seq),
             ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim,
-            float(scale), int(window or 0), B, splits, warps, ptr(status_word(q.device)), stream()),
+            float(scale), int(window or 0), B, splits, warps, float(softcap or 0.0), ptr(slopes),
+            ptr(status_word(q.device)), stream()),
           f"attention_decode_warps (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
     return out
 
@@ -521,7 +525,8 @@ def branch_norm_add(h: torch.Tensor, branches, post_weight: torch.Tensor, eps: f
         h += rms(m) * post_weight (+ extra)
         returns rms(h) * next_weight in the compute dtype if ``next_weight`` is given, else None
 
-    with rms(x) = x / sqrt(mean(x^2) + eps).  The branches are float32 [T, H]; all weight vectors share one dtype.
+    with rms(x) = x / sqrt(mean(x^2) + eps).  A branch is float32 [T, H], or a stack [S, T, H] of partial sums of a K-split
+    product, which are added here in index order; all weight vectors share one dtype.
     """
     need(len(branches) in (1, 2), "branch_norm_add: one or two branches")
     a0, w0 = branches[0]
@@ -532,14 +537,16 @@ def branch_norm_add(h: torch.Tensor, branches, post_weight: torch.Tensor, eps: f
     T, H = h.shape
     need(h.dtype == torch.float32 and h.is_contiguous(), "branch_norm_add: h must be contiguous float32 [T, H]")
     for a in (a0, a1):
-        need(a is None or (a.dtype == torch.float32 and a.shape == (T, H) and a.is_contiguous()),
-             "branch_norm_add: a branch must be contiguous float32 [T, H]")
+        need(a is None or (a.dtype == torch.float32 and tuple(a.shape[-2:]) == (T, H) and a.dim() in (2, 3) and a.is_contiguous()),
+             "branch_norm_add: a branch must be contiguous float32 [T, H] or [S, T, H]")
+    n0 = a0.shape[0] if a0.dim() == 3 else 1
+    n1 = (a1.shape[0] if a1.dim() == 3 else 1) if a1 is not None else 0
     need(all(v.shape == (H,) and v.dtype == vecs[0].dtype and v.is_contiguous() for v in vecs)
          and vecs[0].dtype in (torch.float32, torch.bfloat16), "branch_norm_add: weight vectors must be [H] of one dtype")
     y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if next_weight is not None else None
-    f = _f("elementwise", "rf_branch_norm_add", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p)
-    check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), ptr(w0), ptr(a1), ptr(w1), ptr(post_weight), ptr(extra),
+    f = _f("elementwise", "rf_branch_norm_add", c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), n0, ptr(w0), ptr(a1), n1, ptr(w1), ptr(post_weight), ptr(extra),
             ptr(next_weight), ptr(y), int(vecs[0].dtype == torch.float32), float(eps), T, H, stream()),
           f"branch_norm_add (H={H})")
     return y
@@ -641,6 +648,36 @@ def retention_scan(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay
            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(v.dtype), ptr(qk[0]), ptr(qk[1]), ptr(v), v.stride(0), ptr(state), ptr(decay), ptr(o), ptr(cu_q),
             ptr(seq_slot), B, heads, dim, vdim, stream()), f"retention_scan (heads={heads}, dim={dim}, vdim={vdim})")
+    return o
+
+
+RETENTION_CHUNK = 64
+
+
+def retention_chunked(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, table: torch.Tensor,
+                      cu_q: torch.Tensor, seq_slot: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """What ``retention_scan`` computes, for prompts: the recurrence in chunks of 64 tokens that run side by side (per-chunk
+    sums, then the states between the chunks one after the other, then every chunk's outputs from its start state), all
+    in 32-bit.  ``table``: int32, first[B+1] (index of each sequence's first chunk) followed by (sequence, first row among
+    the sequence's new tokens) of every chunk, in the order of the sequences.  Differs from the scan by rounding only."""
+    need_cuda(qk, v, state, decay, table, cu_q, seq_slot)
+    T = qk.shape[1]
+    B = seq_slot.shape[0]
+    need(qk.dtype == torch.float32 and qk.is_contiguous() and qk.shape == (2, T, heads * dim), "retention_chunked: bad q/k")
+    need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "retention_chunked: v must be [T, heads*vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+         "retention_chunked: state must be float32 [slots, heads, dim, vdim]")
+    need(decay.dtype == torch.float32 and decay.shape == (heads,), "retention_chunked: decay must be float32 [heads]")
+    need(table.dtype == torch.int32 and (table.numel() - (B + 1)) % 2 == 0 and table.numel() > B + 1,
+         "retention_chunked: the chunk table must hold first[B+1] and a pair per chunk")
+    n_chunks = (table.numel() - (B + 1)) // 2
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qk.device)
+    scratch = torch.empty((n_chunks, heads, dim, vdim), dtype=torch.float32, device=qk.device)
+    f = _f("retention", "rf_retention_chunked", c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(v.dtype), ptr(qk[0]), ptr(qk[1]), ptr(v), v.stride(0), ptr(state), ptr(decay), ptr(o), ptr(scratch),
+            ptr(table), n_chunks, ptr(cu_q), ptr(seq_slot), B, heads, dim, vdim, stream()),
+          f"retention_chunked (heads={heads}, dim={dim}, vdim={vdim})")
     return o
 
 

@@ -33,8 +33,8 @@ class GQAAttention(Mixer):
     (one slope per head: after the cap a score is lowered by slope * (query position - key position)), and ``names``
     (the tensors' names below the part's prefix, keys q, k, v, o).  Normed heads and values of another size go into the
     cache through the per-head writer; a cap and slopes are known to the generic attention and to the tcgen05 prompt
-    attention (heads of 64 or 128 with values of the same size), so prompts of such a mixer run on the tensor cores and
-    its single-token steps on the generic kernel.
+    attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
+    on the same kernels as one without them.
     """
 
     accepts_scaled_rows = True
@@ -136,7 +136,7 @@ class GQAAttention(Mixer):
 
     def output(self, ctx, y, cache_view):
         q = self.project_into_cache(ctx, y, cache_view)
-        return self.o(ctx, self.attend(ctx, q, cache_view), out_f32=True)
+        return self.o.f32_parts(ctx, self.attend(ctx, q, cache_view))
 
     def _project_plain(self, ctx, y, view, rot, inv_freq):
         """The projection for heads that are normed or values of another size: one product (K-split partial sums with
@@ -202,7 +202,7 @@ class GQAAttention(Mixer):
         tiles64, tiles128 = ctx.tables.get("attention_tiles64"), ctx.tables.get("attention_tiles128")
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
         shaped = dict(softcap=self.softcap, slopes=self.slopes_dev)
-        if self.v_head_dim != hd or (self.shaped_scores and (ctx.is_decode or ctx.compute_dtype != torch.bfloat16)):
+        if self.v_head_dim != hd or (self.shaped_scores and ctx.compute_dtype != torch.bfloat16):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
                                              ctx.seq_slot, view.block_table, self.scale, view.window,
                                              v_head_dim=self.v_head_dim, **shaped)
@@ -214,8 +214,8 @@ class GQAAttention(Mixer):
                 return kernels.attention_decode_warps(
                     q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                     view.block_table, self.scale, view.window,
-                    splits=kernels.decode_splits(ctx.B, nkv, longest, view.window))
-            if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
+                    splits=kernels.decode_splits(ctx.B, nkv, longest, view.window), **shaped)
+            if not self.shaped_scores and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
                 # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
                 max_chunks = 1

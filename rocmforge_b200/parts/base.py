@@ -97,8 +97,9 @@ class Mixer(Part):
         raise NotImplementedError
 
     def output(self, ctx, y: torch.Tensor, cache_view):
-        """The mixer's result as float32 [T, H] instead of an update of the stream, for blocks that do something to
-        it first (norm it, merge it with another mixer's).  A mixer that offers only ``forward`` cannot sit in those."""
+        """The mixer's result as float32 [T, H] (or as a stack [S, T, H] of partial sums, to be added in index order, or as
+        a ``NormedMean``) instead of an update of the stream, for blocks that do something to it first (norm it, merge it
+        with another mixer's).  A mixer that offers only ``forward`` cannot sit in those."""
         raise NotImplementedError(f"{type(self).__name__} does not hand out its result (only forward)")
 
 

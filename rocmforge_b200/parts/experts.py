@@ -65,7 +65,7 @@ class RoutedExperts(FeedForward):
         if isinstance(y, ScaledRows):
             y = y.materialize()
         T = y.shape[0]
-        z = kernels.gemm_simt(y, self.router_w, self.router_b, out_f32=True)                 # 32-bit sums, any shape
+        z = ctx.matmul(y, self.router_w, self.router_b, out_f32=True)         # 32-bit sums of exact products
         idx, w = kernels.moe_route(z, self.top)
         n = T * self.top
         tc = kernels.tensor_core

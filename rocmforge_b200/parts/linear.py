@@ -25,6 +25,11 @@ class Linear:
         """x [M, K] -> [M, N] in the compute dtype (or float32)."""
         return ctx.matmul(x, self.weight, self.bias, out_f32=out_f32)
 
+    def f32_parts(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        """x W^T in 32-bit as [M, N], or, with few tokens, as a stack [S, M, N] of partial sums over K ranges that the
+        consumer adds in index order (so that every SM streams a share of the weight)."""
+        return ctx.matmul_f32_parts(x, self.weight)
+
     def add_to_stream(self, ctx, x: torch.Tensor, stream) -> None:
         """stream += x W^T: the product lands in the residual stream, in 32-bit."""
         ctx.matmul_residual(x, self.weight, self.bias, stream)

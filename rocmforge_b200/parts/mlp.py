@@ -52,7 +52,7 @@ class GatedMLP(FeedForward):
         self.down.add_to_stream(ctx, a, stream)
 
     def output(self, ctx, y):
-        return self.down(ctx, ctx.gated_activation(y, self.gate_up), out_f32=True)
+        return self.down.f32_parts(ctx, ctx.gated_activation(y, self.gate_up))
 
 
 @FEED_FORWARDS.register("relu2_mlp")
@@ -87,4 +87,4 @@ class SquaredReluMLP(FeedForward):
         self.down.add_to_stream(ctx, self.activated(ctx, y), stream)
 
     def output(self, ctx, y):
-        return self.down(ctx, self.activated(ctx, y), out_f32=True)
+        return self.down.f32_parts(ctx, self.activated(ctx, y))

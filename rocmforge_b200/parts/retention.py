@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Dict, Optional, Sequence
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -65,6 +66,23 @@ class Retention(Mixer):
     def cache_request(self):
         return StateRequest.of(S=((self.n_heads, self.dim, self.vdim), torch.float32))
 
+    # Prompts run the recurrence in chunks side by side; steps of few tokens per sequence run it token by token.
+    CHUNKED_FROM = 17            # tokens of the step's longest portion from which the chunked kernels are taken
+
+    def step_table_names(self):
+        return ("retention_chunks",)
+
+    def step_table(self, name, batch):
+        """first[B+1] (index of each sequence's first chunk), then (sequence, first row) of every chunk of 64 new tokens;
+        empty for steps that take the token-by-token kernel."""
+        if batch.is_decode or batch.max_new < self.CHUNKED_FROM:
+            return np.zeros((0,), dtype=np.int32)
+        C = kernels.RETENTION_CHUNK
+        counts = [(int(n) + C - 1) // C for n in batch.n_new]
+        first = np.concatenate([[0], np.cumsum(counts)])
+        pairs = [(b, q0) for b in range(batch.B) for q0 in range(0, int(batch.n_new[b]), C)]
+        return np.concatenate([first, np.asarray(pairs, dtype=np.int64).reshape(-1)]).astype(np.int32)
+
     def gated(self, ctx, y, state_view):
         """The gated, normed heads [T, heads*vdim] in the compute dtype (the output product's input)."""
         if isinstance(y, ScaledRows):
@@ -77,12 +95,17 @@ class Retention(Mixer):
                                        ctx.tok_pos, self.k_scale)
         v = p[:, 2 * self.qk_size: 2 * self.qk_size + self.v_size]
         g = p[:, 2 * self.qk_size + self.v_size:]
-        o = kernels.retention_scan(qk, v, state_view["S"], self.decay_dev, ctx.cu_q, ctx.seq_slot, self.n_heads,
-                                   self.dim, self.vdim)
+        table = ctx.tables.get("retention_chunks")
+        if table is not None and table.numel() > 0:
+            o = kernels.retention_chunked(qk, v, state_view["S"], self.decay_dev, table, ctx.cu_q, ctx.seq_slot,
+                                          self.n_heads, self.dim, self.vdim)
+        else:
+            o = kernels.retention_scan(qk, v, state_view["S"], self.decay_dev, ctx.cu_q, ctx.seq_slot, self.n_heads,
+                                       self.dim, self.vdim)
         return kernels.retention_gate(o, g, self.n_heads, self.vdim, self.eps)
 
     def forward(self, ctx, y, cache_view, stream):
         self.o.add_to_stream(ctx, self.gated(ctx, y, cache_view), stream)
 
     def output(self, ctx, y, cache_view):
-        return self.o(ctx, self.gated(ctx, y, cache_view), out_f32=True)
+        return self.o.f32_parts(ctx, self.gated(ctx, y, cache_view))

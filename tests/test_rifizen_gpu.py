@@ -374,6 +374,11 @@ def test_branch_norm_add_against_torch(H):
         want_h = f(h) + P.rms_norm(m, f(wp), eps) + f(ex)
         assert (f(h2) - want_h).abs().max() < 1e-4
         assert (f(y) - P.rms_norm(want_h, f(wn), eps)).abs().max() < 1e-4
+        # a branch as a stack of partial sums
+        h4 = h.clone()
+        parts = torch.stack([a * 0.5, a * 0.25, a * 0.25])
+        kernels.branch_norm_add(h4, [(parts, wa), (b, wb)], wp, eps, torch.float32, extra=ex)
+        assert (f(h4) - want_h).abs().max() < 1e-4
         # one branch, nothing else
         h3 = h.clone()
         assert kernels.branch_norm_add(h3, [(a, None)], wp, eps, torch.float32) is None
@@ -497,4 +502,59 @@ def test_tensor_core_prompt_attention_with_cap_and_slopes(hd):
     got = kernels.attention_prefill_tc(q, nh, nkv, hd, kp, vp, i32([x for t in tiles for x in t]), i32([0, 1]), i32(starts), i32(lens),
                                        i32([0, lens[0], T]), bt, scale, window, softcap=cap, slopes=slopes)
     assert (got.float() - want.float()).abs().max() < 3e-2
+    kernels.tensor_core.check_status(dev)
+
+
+@pytest.mark.parametrize("dim,vdim,heads", [(24, 12, 2), (128, 128, 2), (200, 70, 1)])
+def test_chunked_retention_against_the_token_by_token_kernel(dim, vdim, heads):
+    """Prompts of 1 to 300 new tokens in one step (chunks of 64 side by side, states carried between them, a state that an
+    earlier step left) against the scan; the two differ by rounding alone."""
+    from rocmforge_b200 import kernels
+    torch.manual_seed(dim)
+    dev = "cuda"
+    lens = [300, 1, 64, 65, 130]
+    T, B = sum(lens), len(lens)
+    decay = torch.tensor(([1.0, 0.6, 0.999] * 3)[:heads], dtype=torch.float32, device=dev)
+    state0 = torch.randn(B + 2, heads, dim, vdim, device=dev)
+    qk = torch.randn(2, T, heads * dim, device=dev) * dim ** -0.5
+    v = torch.randn(T, heads * vdim, device=dev)
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=dev)
+    slots = torch.tensor([3, 0, 6, 1, 4], dtype=torch.int32, device=dev)
+    s_scan, s_chunk = state0.clone(), state0.clone()
+    want = kernels.retention_scan(qk, v, s_scan, decay, cu, slots, heads, dim, vdim)
+    counts = [(n + 63) // 64 for n in lens]
+    table = list(np.concatenate([[0], np.cumsum(counts)])) + [x for b, n in enumerate(lens) for q0 in range(0, n, 64) for x in (b, q0)]
+    got = kernels.retention_chunked(qk, v, s_chunk, decay, torch.tensor(table, dtype=torch.int32, device=dev), cu, slots, heads, dim, vdim)
+    assert (got - want).abs().max() <= 2e-5 * want.abs().max()
+    assert (s_chunk - s_scan).abs().max() <= 2e-5 * s_scan.abs().max()
+    assert torch.equal(s_chunk[2], state0[2]) and torch.equal(s_chunk[5], state0[5])        # slots of no sequence of the step
+
+
+@pytest.mark.parametrize("hd,nh,nkv", [(64, 8, 2), (128, 4, 4), (128, 6, 1)])
+def test_clustered_decode_attention_with_cap_and_slopes(hd, nh, nkv):
+    """bfloat16, one new token per sequence at contexts of 1 to 700 with a window of 300, capped scores and distance
+    slopes: the clustered kernel (1, 2 and 4 CTAs a pair) against the generic one."""
+    from rocmforge_b200 import kernels
+    torch.manual_seed(hd + nh)
+    dev, window, cap, scale = "cuda", 300, 6.0, 0.4
+    ctx_len = [1, 63, 64, 65, 299, 300, 301, 700]
+    B = len(ctx_len)
+    n_pages = [(t + 63) // 64 for t in ctx_len]
+    kp = (torch.randn(sum(n_pages) + 1, nkv, 64, hd, device=dev)).to(torch.bfloat16)
+    vp = (torch.randn(sum(n_pages) + 1, nkv, 64, hd, device=dev)).to(torch.bfloat16)
+    bt = torch.zeros(B, max(n_pages), dtype=torch.int32, device=dev)
+    page = 1
+    for b in range(B):
+        for p in range(n_pages[b]):
+            bt[b, p] = page
+            page += 1
+    q = (torch.randn(B, nh * hd, device=dev) * 0.5).to(torch.bfloat16)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    tok_seq, tok_pos, slot = i32(list(range(B))), i32([t - 1 for t in ctx_len]), i32(list(range(B)))
+    slopes = torch.tensor(P.distance_slopes(nh), dtype=torch.float32, device=dev) * 4
+    want = kernels.attention_generic(q, nh, nkv, hd, kp, vp, tok_seq, tok_pos, slot, bt, scale, window, softcap=cap, slopes=slopes)
+    for splits in (1, 2, 4):
+        got = kernels.attention_decode_warps(q, nh, nkv, hd, kp, vp, tok_seq, tok_pos, slot, bt, scale, window, splits=splits,
+                                             softcap=cap, slopes=slopes)
+        assert (got.float() - want.float()).abs().max() < 3e-2, f"{splits} CTAs a pair"
     kernels.tensor_core.check_status(dev)
