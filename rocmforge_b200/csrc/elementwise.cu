@@ -492,7 +492,7 @@ __global__ void add_row_kernel(float* __restrict__ h, const T* __restrict__ vec,
 // with rms(x) = x / sqrt(mean(x^2) + eps).  A branch comes as n0 (n1) partial sums [n][rows][H] of a K-split product,
 // added here in index order.  A block per row; the rows stay in shared memory between the passes.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int n0, const void* __restrict__ w0,
                        const float* __restrict__ a1, int n1, size_t part_stride, const void* __restrict__ w1,
                        const void* __restrict__ w_post, const void* __restrict__ extra, const void* __restrict__ w_next,
@@ -508,7 +508,9 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int 
         float s0 = 0.f, s1 = 0.f;
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
             float x = 0.f, z = 0.f;
+#pragma unroll 4
             for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
+#pragma unroll 4
             for (int s = 0; s < n1; ++s) z += a1[(size_t)s * part_stride + base + c];
             row[c] = x; other[c] = z;
             s0 += x * x; s1 += z * z;
@@ -520,6 +522,7 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int 
     } else {
         for (int c = threadIdx.x; c < H; c += blockDim.x) {
             float x = 0.f;
+#pragma unroll 4
             for (int s = 0; s < n0; ++s) x += a0[(size_t)s * part_stride + base + c];
             row[c] = x;
         }
@@ -566,7 +569,7 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
     const int rh = rot_dim >> 1;
     pdl_wait();
     const int n_heads_all = write_kv ? nh + 2 * nkv : nh;
-    for (int head = warp; head < n_heads_all; head += nwarp) {
+    for (int head = blockIdx.y * nwarp + warp; head < n_heads_all; head += gridDim.y * nwarp) {
         const bool is_v = head >= nh + nkv;
         const int n = is_v ? hdv : hd;
         const int col = is_v ? (nh + nkv) * hd + (head - nh - nkv) * hdv : head * hd;
@@ -576,6 +579,7 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
             if (PARTIALS) {
                 const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride + col + e;
                 x = 0.f;
+#pragma unroll 4
                 for (int sp = 0; sp < n_partials; ++sp) x += p[(size_t)sp * partial_stride];
             } else {
                 x = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col + e]);
@@ -753,7 +757,10 @@ static int launch_branch_norm_add(float* h, const float* a0, int n0, const void*
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    rf_launch(branch_norm_add_kernel<T>, dim3(rows), dim3(256), smem, st, h, a0, n0, w0, a1, n1, (size_t)rows * H, w1, w_post,
+    // few rows (decode): a row's columns over up to 1024 threads, so that its loads are all in flight at once
+    int threads = 256;
+    if (rows <= 296) { threads = (H + 31) / 32 * 32; if (threads > 1024) threads = 1024; if (threads < 256) threads = 256; }
+    rf_launch(branch_norm_add_kernel<T>, dim3(rows), dim3(threads), smem, st, h, a0, n0, w0, a1, n1, (size_t)rows * H, w1, w_post,
               extra, w_next, reinterpret_cast<T*>(y_next), w_is_f32, eps, H);
     RF_LAUNCH_CHECK();
     return 0;
@@ -769,12 +776,16 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
     if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0) return RF_ERR_BAD_ARG;
     const size_t smem = (size_t)4 * (hd > hdv ? hd : hdv) * sizeof(float);
     if (smem > 48 * 1024) return RF_ERR_UNSUPPORTED;
+    // few tokens: a token's heads over several blocks (a warp per head)
+    const int all_heads = write_kv ? nh + 2 * nkv : nh;
+    int by = T_ >= 512 ? 1 : (all_heads + 3) / 4;
+    if (by > 64) by = 64;
     if (n_partials > 0)
-        rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
+        rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_, by), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
     else
-        rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
+        rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_, by), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                   max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
     RF_LAUNCH_CHECK();

@@ -28,7 +28,7 @@ __global__ void retention_prepare_kernel(const T* __restrict__ src, int row_stri
     const int pos = tok_pos[t];
     const int rh = rot_dim >> 1;
     pdl_wait();
-    for (int idx = threadIdx.x; idx < 2 * width; idx += blockDim.x) {
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < 2 * width; idx += gridDim.y * blockDim.x) {
         const int which = idx >= width;                       // 0: q, 1: k
         const int c = idx - which * width, e = c % dim;
         const T* row = src + (size_t)t * row_stride + (which ? k_col : q_col);
@@ -199,7 +199,8 @@ retention_chunk_state_kernel(const float* __restrict__ k, const T* __restrict__ 
 }
 
 // grid (sequence, head, blocks over dim * vdim); a thread owns one element of the state through all chunks
-__global__ void retention_chunk_carry_kernel(float* __restrict__ LS, float* __restrict__ state, const float* __restrict__ decay,
+__global__ void __launch_bounds__(256)
+retention_chunk_carry_kernel(float* __restrict__ LS, float* __restrict__ state, const float* __restrict__ decay,
                                              const int* __restrict__ table, const int* __restrict__ cu_q,
                                              const int* __restrict__ seq_slot, int heads, int dim, int vdim) {
     pdl_trigger();
@@ -213,12 +214,20 @@ __global__ void retention_chunk_carry_kernel(float* __restrict__ LS, float* __re
     float* S = state + (((size_t)seq_slot[b] * heads + h) * dim) * vdim + e;
     pdl_wait();
     float s = *S;
-    for (int c = c0; c < c1; ++c) {
-        float* p = LS + (((size_t)c * heads + h) * dim) * vdim + e;
-        const float l = *p;
-        *p = s;                                          // the state before chunk c
-        const int cnt = min(RC, n_new - (c - c0) * RC);
-        s = fmaf(cnt == RC ? d_full : powf(d, (float)cnt), s, l);
+    const size_t step = (size_t)heads * dim * vdim;
+    float* p = LS + (((size_t)c0 * heads + h) * dim) * vdim + e;
+    for (int c = c0; c < c1; c += 8) {                   // eight chunks' sums on their way at once; the chain is the FMAs alone
+        float l[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) l[u] = (c + u < c1) ? p[(size_t)u * step] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (c + u < c1) {
+                p[(size_t)u * step] = s;                 // the state before chunk c + u
+                const int cnt = min(RC, n_new - (c + u - c0) * RC);
+                s = fmaf(cnt == RC ? d_full : powf(d, (float)cnt), s, l[u]);
+            }
+        p += 8 * step;
     }
     *S = s;
 }
@@ -359,7 +368,10 @@ static int launch_prepare(const void* src, int row_stride, int q_col, int k_col,
                           int rot_dim, const float* inv_freq, const int* tok_pos, float k_scale, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (rot_dim < 0 || rot_dim % 2 || rot_dim > dim) return RF_ERR_BAD_ARG;
-    rf_launch(retention_prepare_kernel<T>, dim3(T_), dim3(256), 0, st, reinterpret_cast<const T*>(src), row_stride, q_col, k_col,
+    // few tokens: a row's elements over several blocks, so that the sines and cosines of a row do not queue in one
+    int by = T_ >= 512 ? 1 : (2 * heads * dim + 255) / 256;
+    if (by > 64) by = 64;
+    rf_launch(retention_prepare_kernel<T>, dim3(T_, by), dim3(256), 0, st, reinterpret_cast<const T*>(src), row_stride, q_col, k_col,
               qk, heads, dim, rot_dim, inv_freq, tok_pos, k_scale, T_);
     RF_LAUNCH_CHECK();
     return 0;
