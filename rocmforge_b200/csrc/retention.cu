@@ -6,6 +6,8 @@
 //
 //   retention_prepare   q, k of the projection's row -> rotated (first rot_dim elements of a head, pairs
 //                       (i, i + rot_dim/2), angle float(pos) * inv_freq[i]), k scaled, as float [2, T, heads*dim]
+//   The state of a (sequence, head) is kept as [vdim][dim]: a column of S (one value dimension) is contiguous, so a
+//   warp that owns a column reads and writes whole 128-byte lines.
 //   retention_scan      the recurrence, token by token: a block owns (sequence, head, a slice of 8 value columns);
 //                       the columns of S are independent of each other, so the slices never talk.  A warp owns one
 //                       column; a lane holds the rows lane, lane + 32, ... of it in registers.  The order of every sum
@@ -64,13 +66,13 @@ retention_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, 
     const int slot = seq_slot[b];
     const float d = decay[h];
     const int width = heads * dim;
-    float* S = state + (((size_t)slot * heads + h) * dim) * vdim;
+    float* S = state + (((size_t)slot * heads + h) * vdim + (j < vdim ? j : 0)) * dim;      // this warp's column
     pdl_wait();
     float s[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int i = lane + 32 * r;
-        s[r] = (i < dim && j < vdim) ? S[(size_t)i * vdim + j] : 0.f;
+        s[r] = (i < dim && j < vdim) ? S[i] : 0.f;
     }
     for (int t0 = row0; t0 < row1; t0 += RT_TOK) {
         const int cnt = min(RT_TOK, row1 - t0);
@@ -105,7 +107,7 @@ retention_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, 
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             const int i = lane + 32 * r;
-            if (i < dim) S[(size_t)i * vdim + j] = s[r];
+            if (i < dim) S[i] = s[r];
         }
     }
 }
@@ -146,25 +148,29 @@ __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __re
 #define RC_LD 68              // row stride of the transposed tiles: rows stay 16-byte aligned
 #define RV 64                 // value columns of a block
 
-// grid (chunk, head, ceil(vdim / RV)); 256 threads: thread (ty, tx) owns rows ty + 16 r and columns 4 tx .. 4 tx + 3
+// grid (chunk, head, ceil(vdim / RV)); 256 threads: thread (ty, tx) owns rows ty * RPT .. + RPT - 1 (RPT = 4, 8, 12 or 16
+// by dim) and columns 4 tx .. 4 tx + 3: per key, 16-byte loads of its k rows and of its v columns feed 4 RPT FMAs
 template <typename T>
 __global__ void __launch_bounds__(256)
 retention_chunk_state_kernel(const float* __restrict__ k, const T* __restrict__ v, int v_stride, float* __restrict__ LS,
                              const float* __restrict__ decay, const int* __restrict__ table, const int* __restrict__ cu_q,
                              int B, int heads, int dim, int vdim) {
     extern __shared__ __align__(16) float sh[];
-    float* ks = sh;                                   // [RC][dim], already times d^(cnt-1-s)
-    float* vs = ks + RC * dim;                        // [RC][RV]
+    const int dimP = (dim + 3) & ~3;                  // rows of 16-byte groups
+    float* ks = sh;                                   // [RC][dimP], already times d^(cnt-1-s)
+    float* vs = ks + RC * dimP;                       // [RC][RV]
+    float* pw = vs + RC * RV;                         // d^0 .. d^(RC-1)
     pdl_trigger();
     const int c = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * RV;
     const int b = table[B + 1 + 2 * c], q0 = table[B + 2 + 2 * c];
     const int row0 = cu_q[b] + q0, cnt = min(RC, cu_q[b + 1] - row0);
-    const float d = decay[h];
     const int width = heads * dim;
+    if (threadIdx.x < RC) pw[threadIdx.x] = powf(decay[h], (float)threadIdx.x);
     pdl_wait();
-    for (int idx = threadIdx.x; idx < cnt * dim; idx += 256) {
-        const int s = idx / dim, i = idx - s * dim;
-        ks[idx] = k[(size_t)(row0 + s) * width + h * dim + i] * powf(d, (float)(cnt - 1 - s));
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < cnt * dimP; idx += 256) {
+        const int s = idx / dimP, i = idx - s * dimP;
+        ks[idx] = i < dim ? k[(size_t)(row0 + s) * width + h * dim + i] * pw[cnt - 1 - s] : 0.f;
     }
     for (int idx = threadIdx.x; idx < cnt * RV; idx += 256) {
         const int s = idx / RV, j = idx - s * RV;
@@ -172,26 +178,31 @@ retention_chunk_state_kernel(const float* __restrict__ k, const T* __restrict__ 
     }
     __syncthreads();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int groups = (dim + 63) / 64;               // 16-byte groups of rows per thread
+    const int i0 = ty * 4 * groups;
     float acc[16][4];
 #pragma unroll
     for (int r = 0; r < 16; ++r) { acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f; }
     for (int s = 0; s < cnt; ++s) {
         const float4 vv = *reinterpret_cast<const float4*>(&vs[s * RV + 4 * tx]);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int i = ty + 16 * r;
-            if (i < dim) {
-                const float kk = ks[s * dim + i];
-                acc[r][0] = fmaf(kk, vv.x, acc[r][0]); acc[r][1] = fmaf(kk, vv.y, acc[r][1]);
-                acc[r][2] = fmaf(kk, vv.z, acc[r][2]); acc[r][3] = fmaf(kk, vv.w, acc[r][3]);
+        for (int g = 0; g < 4; ++g) {
+            if (g < groups && i0 + 4 * g < dimP) {
+                const float4 kk = *reinterpret_cast<const float4*>(&ks[s * dimP + i0 + 4 * g]);
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    acc[4 * g + x][0] = fmaf(kv[x], vv.x, acc[4 * g + x][0]); acc[4 * g + x][1] = fmaf(kv[x], vv.y, acc[4 * g + x][1]);
+                    acc[4 * g + x][2] = fmaf(kv[x], vv.z, acc[4 * g + x][2]); acc[4 * g + x][3] = fmaf(kv[x], vv.w, acc[4 * g + x][3]);
+                }
             }
         }
     }
     float* out = LS + (((size_t)c * heads + h) * dim) * vdim;
 #pragma unroll
     for (int r = 0; r < 16; ++r) {
-        const int i = ty + 16 * r;
-        if (i < dim)
+        const int i = i0 + r;
+        if (r < 4 * groups && i < dim)
 #pragma unroll
             for (int u = 0; u < 4; ++u)
                 if (j0 + 4 * tx + u < vdim) out[(size_t)i * vdim + j0 + 4 * tx + u] = acc[r][u];
@@ -211,7 +222,7 @@ retention_chunk_carry_kernel(float* __restrict__ LS, float* __restrict__ state, 
     const int n_new = cu_q[b + 1] - cu_q[b];
     const float d = decay[h];
     const float d_full = powf(d, (float)RC);
-    float* S = state + (((size_t)seq_slot[b] * heads + h) * dim) * vdim + e;
+    float* S = state + (((size_t)seq_slot[b] * heads + h) * vdim + e % vdim) * dim + e / vdim;     // kept as [vdim][dim]
     pdl_wait();
     float s = *S;
     const size_t step = (size_t)heads * dim * vdim;
@@ -338,7 +349,7 @@ static int launch_chunked(const float* q, const float* k, const void* v, int v_s
     if (B <= 0 || n_chunks <= 0) return 0;
     if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
     const int vz = (vdim + RV - 1) / RV;
-    const size_t smem1 = (size_t)(RC * dim + RC * RV) * sizeof(float);
+    const size_t smem1 = (size_t)(RC * ((dim + 3) & ~3) + RC * RV + RC) * sizeof(float);
     const size_t smem3 = (size_t)(2 * dim * RC_LD + RC * RV + RC * RC_LD + RC + 4) * sizeof(float);
     static size_t set1 = 48 * 1024, set3 = 48 * 1024;
     if (smem1 > set1) {

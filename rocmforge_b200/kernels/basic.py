@@ -632,15 +632,16 @@ def retention_prepare(proj: torch.Tensor, q_col: int, k_col: int, heads: int, di
 
 def retention_scan(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, cu_q: torch.Tensor,
                    seq_slot: torch.Tensor, heads: int, dim: int, vdim: int) -> torch.Tensor:
-    """S <- decay_h S + k v^T, o = S^T q, token by token for every sequence of the step; ``state`` [slots, heads, dim,
-    vdim] float32 is read at the step's start and left as after its last token.  ``v`` is a [T, heads*vdim] view (rows
+    """S <- decay_h S + k v^T, o = S^T q, token by token for every sequence of the step; ``state`` [slots, heads, vdim,
+    dim] float32 (S transposed: a value dimension's column is contiguous) is read at the step's start and left as after
+    its last token.  ``v`` is a [T, heads*vdim] view (rows
     may be strided).  Returns o float32 [T, heads*vdim]."""
     need_cuda(qk, v, state, decay, cu_q, seq_slot)
     T = qk.shape[1]
     need(qk.dtype == torch.float32 and qk.is_contiguous() and qk.shape == (2, T, heads * dim), "retention_scan: bad q/k")
     need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "retention_scan: v must be [T, heads*vdim]")
-    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
-         "retention_scan: state must be float32 [slots, heads, dim, vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
+         "retention_scan: state must be float32 [slots, heads, vdim, dim]")
     need(decay.dtype == torch.float32 and decay.shape == (heads,), "retention_scan: decay must be float32 [heads]")
     B = seq_slot.shape[0]
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qk.device)
@@ -665,8 +666,8 @@ def retention_chunked(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, de
     B = seq_slot.shape[0]
     need(qk.dtype == torch.float32 and qk.is_contiguous() and qk.shape == (2, T, heads * dim), "retention_chunked: bad q/k")
     need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "retention_chunked: v must be [T, heads*vdim]")
-    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
-         "retention_chunked: state must be float32 [slots, heads, dim, vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
+         "retention_chunked: state must be float32 [slots, heads, vdim, dim]")
     need(decay.dtype == torch.float32 and decay.shape == (heads,), "retention_chunked: decay must be float32 [heads]")
     need(table.dtype == torch.int32 and (table.numel() - (B + 1)) % 2 == 0 and table.numel() > B + 1,
          "retention_chunked: the chunk table must hold first[B+1] and a pair per chunk")

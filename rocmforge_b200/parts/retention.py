@@ -18,7 +18,7 @@ from .linear import Linear
 class Retention(Mixer):
     """Per head, with q, k of size ``dim`` and v of size ``vdim``:
 
-        S_t = decay_h * S_(t-1) + k_t v_t^T        (S starts at zero, float32 [dim, vdim], kept per sequence)
+        S_t = decay_h * S_(t-1) + k_t v_t^T        (S starts at zero, float32, kept per sequence as [vdim, dim])
         o_t = S_t^T q_t                            (no softmax, no denominator)
         out = W_o (concat_h(o_t / rms(o_t)) * silu(W_g x))
 
@@ -64,7 +64,7 @@ class Retention(Mixer):
         return ["elementwise", "retention"]
 
     def cache_request(self):
-        return StateRequest.of(S=((self.n_heads, self.dim, self.vdim), torch.float32))
+        return StateRequest.of(S=((self.n_heads, self.vdim, self.dim), torch.float32))
 
     # Prompts run the recurrence in chunks side by side; steps of few tokens per sequence run it token by token.
     CHUNKED_FROM = 17            # tokens of the step's longest portion from which the chunked kernels are taken

@@ -101,7 +101,7 @@ def test_cache_of_side_by_side_mixers():
     assert set(view) == {"left", "right"}
     assert view["left"].k_pages.shape[1:] == (2, 64, 16) and view["left"].v_pages.shape[1:] == (2, 64, 24)
     assert view["left"].window == 7 and cache.view(1)["left"].window == 3
-    assert view["right"]["S"].shape == (3, 2, 24, 12) and view["right"]["S"].dtype == torch.float32
+    assert view["right"]["S"].shape == (3, 2, 12, 24) and view["right"]["S"].dtype == torch.float32
     assert cache.view(2)["right"]["S"].data_ptr() != view["right"]["S"].data_ptr()            # pass 2 of layer 0
     s = cache.alloc_slot()
     view["right"]["S"][s] = 5.0

@@ -300,7 +300,7 @@ def test_retention_scan_against_the_recurrence_and_across_cuts(dim, vdim, heads)
     torch.manual_seed(dim)
     dev, T = "cuda", 700
     decay = torch.tensor(([1.0, 0.5, 0.999] * 3)[:heads], dtype=torch.float32, device=dev)
-    state = torch.zeros(3, heads, dim, vdim, device=dev)
+    state = torch.zeros(3, heads, vdim, dim, device=dev)           # kept transposed: a value dimension's column is contiguous
     qk = torch.randn(2, 2 * T, heads * dim, device=dev) * dim ** -0.5
     v = torch.randn(2 * T, heads * vdim, device=dev)
     v[20] *= 50.0
@@ -318,7 +318,7 @@ def test_retention_scan_against_the_recurrence_and_across_cuts(dim, vdim, heads)
         want[t] = torch.einsum("hdv,hd->hv", S, q64[t])
     got = whole[:T].double().cpu().reshape(T, heads, vdim)
     assert (got - want).abs().max() <= 1e-4 * want.abs().max()
-    assert (end_state[2].double().cpu() - S).abs().max() <= 1e-4 * S.abs().max()
+    assert (end_state[2].double().cpu().transpose(-1, -2) - S).abs().max() <= 1e-4 * S.abs().max()
     assert (state[1] == 0).all()                                  # a slot that no sequence of the step holds
     # the same in portions
     state.zero_()
@@ -515,7 +515,7 @@ def test_chunked_retention_against_the_token_by_token_kernel(dim, vdim, heads):
     lens = [300, 1, 64, 65, 130]
     T, B = sum(lens), len(lens)
     decay = torch.tensor(([1.0, 0.6, 0.999] * 3)[:heads], dtype=torch.float32, device=dev)
-    state0 = torch.randn(B + 2, heads, dim, vdim, device=dev)
+    state0 = torch.randn(B + 2, heads, vdim, dim, device=dev)
     qk = torch.randn(2, T, heads * dim, device=dev) * dim ** -0.5
     v = torch.randn(T, heads * vdim, device=dev)
     cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32, device=dev)
