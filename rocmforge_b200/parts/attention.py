@@ -104,8 +104,10 @@ class GQAAttention(Mixer):
 
     def cuda_modules(self, compute_dtype):
         mods = ["elementwise", "attention_generic"]
-        if compute_dtype == torch.bfloat16:
-            mods += ["attention_decode", "attention_prefill", "attention_prefill_tc"]
+        if compute_dtype == torch.bfloat16 and self.v_head_dim == self.head_dim:
+            mods += ["attention_decode", "attention_prefill_tc"]
+            if not self.shaped_scores:
+                mods.append("attention_prefill")         # the mma.sync prompt kernel knows no cap and no slopes
         return mods
 
     def cache_request(self):

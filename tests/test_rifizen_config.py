@@ -161,3 +161,27 @@ def test_plain_window_and_routing_edges():
     def expert(e):
         return (P.silu(h[0] @ Wm[f"m.e{e}.gate"].T) * (h[0] @ Wm[f"m.e{e}.up"].T)) @ Wm[f"m.e{e}.down"].T
     assert (out[0] - (w[0] * expert(1) + w[1] * expert(3))).abs().max() < 1e-12
+
+
+def test_command_line_writes_a_random_model_folder(tmp_path):
+    """rocmforge --random-config CONFIG --write-random DIR for this design: config.json comes back as it went in, the
+    tensors are those the builder names, and the same seed gives the same bits."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    from safetensors.torch import load_file
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(config_dict(RIFIZEN_CONFIGS["RA"])))
+    outs = []
+    for name in ("a", "b"):
+        out = tmp_path / name
+        r = subprocess.run([sys.executable, f"{ROOT}/bin/rocmforge", "--random-config", str(cfg_path), "--write-random", str(out),
+                            "--random-seed", "5", "--dtype", "float32"], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        outs.append(load_file(str(out / "model.safetensors")))
+    written = json.load(open(tmp_path / "a" / "config.json"))
+    assert {k: v for k, v in written.items() if k != "torch_dtype"} == config_dict(RIFIZEN_CONFIGS["RA"])
+    arch, cfg = parsed(RIFIZEN_CONFIGS["RA"])
+    assert set(outs[0]) == set(arch.build(cfg).param_specs())
+    assert all(torch.equal(outs[0][k], outs[1][k]) for k in outs[0])
+    assert float(outs[0]["l1.mlp.router.b"].abs().max()) > 0 and torch.equal(outs[0]["l0.norm1"], torch.ones(64))
