@@ -85,6 +85,7 @@ class RifizenConfig:
     loop_start: int = 0
     loop_stop: int = 0
     loop_times: int = 1
+    loop_given: bool = False       # config.json has a loop (its table of pass vectors exists even if the stretch is empty)
     raw: dict = field(default_factory=dict, repr=False)
 
     ARCHITECTURE = "Rifizen"
@@ -149,6 +150,7 @@ class RifizenConfig:
                   eps=_get(raw, "norm.eps", float, positive=True), layers=layers, raw=copy.deepcopy(raw))
         loop = raw.get("loop")
         if loop is not None:
+            cfg.loop_given = True
             cfg.loop_start = _get(raw, "loop.start", int, minimum=0)
             cfg.loop_stop = _get(raw, "loop.stop", int, minimum=0)
             cfg.loop_times = _get(raw, "loop.times", int, minimum=1)

@@ -145,7 +145,7 @@ class Model:
         for name, t in random_tensors(specs, seed, dtype, device):
             params[name] = t.to(target_dtype(specs[name], t.dtype, dtype))
         for name, s in specs.items():
-            if name not in params:
+            if name not in params and not s.optional:
                 params[name] = params[s.tied_to]
         return cls(spec, params, dtype, device, options)
 

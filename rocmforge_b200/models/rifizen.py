@@ -59,9 +59,8 @@ def build_rifizen(cfg: RifizenConfig) -> ModelSpec:
         prefixes.append(f"l{i}.")
 
     schedule = [ScheduleEntry(layer=i) for i in range(cfg.loop_start if cfg.has_loop else len(cfg.layers))]
-    offsets = None
+    offsets = PassOffsets(cfg.loop_times, W, param_name="") if cfg.loop_given else None
     if cfg.has_loop:
-        offsets = PassOffsets(cfg.loop_times, W, param_name="")
         for t in range(cfg.loop_times):
             for i in range(cfg.loop_start, cfg.loop_stop):
                 schedule.append(ScheduleEntry(layer=i, pass_index=t if i == cfg.loop_start else None))

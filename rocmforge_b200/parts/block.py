@@ -37,6 +37,17 @@ class PreNormBlock(Block):
         stream.next_norm = None
 
 
+class UnusedTensors(Part):
+    """Tensors that a folder may hold although the model does not use them (the norms of a sub-layer that a layer does not
+    have): they are accepted and left alone."""
+
+    def __init__(self, specs: Dict[str, "ParamSpec"]):
+        self.specs = dict(specs)
+
+    def param_specs(self):
+        return self.specs
+
+
 @BLOCKS.register("sandwich")
 class SandwichBlock(Block):
     """x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))): every sub-layer is normed on its way in and on its way
@@ -65,6 +76,12 @@ class SandwichBlock(Block):
             out[self.names["mixer"]] = self.mixer
         if self.ffn is not None:
             out.update({self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn, self.names["post2"]: self.post2})
+        elif self.names.get("norm2") is not None and self.names.get("post2") is not None:
+            # a layer without feed-forward: a folder that stores the second pair of norms all the same is not at fault
+            from ..weights.spec import ParamSpec
+            size = self.norm1.size
+            out[""] = UnusedTensors({self.names[n] + self.norm1.param_name: ParamSpec((size,), kind="vector", init="ones", optional=True)
+                                     for n in ("norm2", "post2")})
         return out
 
     def entry_norm(self):

@@ -58,7 +58,7 @@ def check_folder(files: ModelFiles, specs: Dict[str, ParamSpec]) -> None:
     have = set(files.names())
     for name, spec in specs.items():
         if name not in have:
-            if spec.tied_to is not None and spec.tied_to in have:
+            if (spec.tied_to is not None and spec.tied_to in have) or spec.optional:
                 continue
             missing.append(name)
             continue
@@ -89,7 +89,7 @@ def load_folder(folder: str, specs: Dict[str, ParamSpec], compute_dtype: torch.d
         src = files.tensor(name)
         out[name] = src.to(device=device, dtype=target_dtype(spec, src.dtype, compute_dtype)).contiguous()
     for name, spec in specs.items():
-        if name not in out:
+        if name not in out and not spec.optional:
             # src/gpu/weights.rs:868-886 makes a second copy for a tied head; an alias is enough
             out[name] = out[spec.tied_to]
     return out

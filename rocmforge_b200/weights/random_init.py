@@ -129,7 +129,7 @@ def random_tensors(specs: Dict[str, ParamSpec], seed: int, dtype: torch.dtype,
                    device="cpu") -> Iterator[Tuple[str, torch.Tensor]]:
     """(name, tensor) for every spec that is not left to its tied partner."""
     for name, spec in specs.items():
-        if spec.tied_to is not None:
+        if spec.tied_to is not None or spec.optional:
             continue
         yield name, random_tensor(name, spec, seed, dtype, device)
 

@@ -15,9 +15,12 @@ class ParamSpec:
              "int_table": integer table, kept as int32.
     init     how the random-weights mode fills it: "normal" (mean 0, ``std``), "ones", "zeros".
     tied_to  full name of another tensor that stands in when this one is absent.
+    optional a tensor that a folder may hold or not (one that the model does not use: a file that has it is not at
+             fault, and the random-weights mode does not make it).
     """
     shape: Tuple[int, ...]
     kind: str = "matrix"
     init: str = "normal"
     std: float = 0.02
     tied_to: Optional[str] = None
+    optional: bool = False

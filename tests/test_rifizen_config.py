@@ -86,8 +86,9 @@ def test_tensor_names_and_shapes():
             "l2.mix.right.q": (40, 64)}
     for name, shape in want.items():
         assert tuple(specs[name].shape) == shape, name
-    assert not any(n.startswith("l2.mlp") or n.startswith("l2.norm2") for n in specs)          # a layer without feed-forward
-    assert len(specs) == 4 + 3 * 13 + (2 + 2) + (2 + 2 + 3 * 5)
+    # a layer without feed-forward: no mlp tensors; its second pair of norms may be in a folder, and is not used
+    assert not any(n.startswith("l2.mlp") for n in specs) and specs["l2.norm2"].optional and specs["l2.norm2b"].optional
+    assert len([n for n, s in specs.items() if not s.optional]) == 4 + 3 * 13 + (2 + 2) + (2 + 2 + 3 * 5)
 
 
 def test_cache_of_side_by_side_mixers():
@@ -182,6 +183,34 @@ def test_command_line_writes_a_random_model_folder(tmp_path):
     written = json.load(open(tmp_path / "a" / "config.json"))
     assert {k: v for k, v in written.items() if k != "torch_dtype"} == config_dict(RIFIZEN_CONFIGS["RA"])
     arch, cfg = parsed(RIFIZEN_CONFIGS["RA"])
-    assert set(outs[0]) == set(arch.build(cfg).param_specs())
+    assert set(outs[0]) == {n for n, s in arch.build(cfg).param_specs().items() if not s.optional}
     assert all(torch.equal(outs[0][k], outs[1][k]) for k in outs[0])
     assert float(outs[0]["l1.mlp.router.b"].abs().max()) > 0 and torch.equal(outs[0]["l0.norm1"], torch.ones(64))
+
+
+def test_a_folder_may_hold_the_unused_norms_and_an_unused_pass_table(tmp_path):
+    """A layer without feed-forward whose second pair of norms is stored all the same, and a loop over an empty stretch of
+    layers whose table of pass vectors is stored: both folders load; a tensor nobody knows is still a fault."""
+    from rocmforge_b200 import WeightError, write_model_folder
+    from rocmforge_b200.weights import load_folder
+    from rocmforge_b200.weights.safetensors_io import write_safetensors
+    from safetensors.torch import load_file
+    raw = copy.deepcopy(config_dict(RIFIZEN_CONFIGS["RA"]))
+    raw["loop"] = {"start": 1, "stop": 1, "times": 2}
+    arch, cfg = parsed(raw)
+    spec = arch.build(cfg)
+    assert [(e.layer, e.pass_index) for e in spec.schedule] == [(0, None), (1, None), (2, None)]
+    folder = str(tmp_path / "m")
+    write_model_folder(folder, raw, spec.param_specs(), 3, torch.float32)
+    tensors = load_file(folder + "/model.safetensors")
+    assert "loop.step" in tensors and "l2.norm2" not in tensors
+    tensors["l2.norm2"] = torch.ones(64)
+    tensors["l2.norm2b"] = torch.ones(64)
+    write_safetensors(folder + "/model.safetensors", tensors.items())
+    loaded = load_folder(folder, spec.param_specs(), torch.float32, "cpu")
+    assert "l2.norm2" in loaded and "l0.mix.left.q" in loaded
+    tensors["l2.norm3"] = torch.ones(64)
+    write_safetensors(folder + "/model.safetensors", tensors.items())
+    with pytest.raises(WeightError) as e:
+        load_folder(folder, spec.param_specs(), torch.float32, "cpu")
+    assert e.value.unexpected == ["l2.norm3"]
