@@ -19,6 +19,8 @@
 #define RT_COLS 8             // value columns (warps) of a scan block
 #define RT_TOK 16             // tokens staged in shared memory at a time
 
+// A thread per unit of a head: a rotated pair (elements e and e + rot_dim/2 of q and of k: one sine and cosine serve all
+// four), or an element beyond the rotated ones.
 template <typename T>
 __global__ void retention_prepare_kernel(const T* __restrict__ src, int row_stride, int q_col, int k_col,
                                          float* __restrict__ qk, int heads, int dim, int rot_dim,
@@ -29,22 +31,29 @@ __global__ void retention_prepare_kernel(const T* __restrict__ src, int row_stri
     const int width = heads * dim;
     const int pos = tok_pos[t];
     const int rh = rot_dim >> 1;
+    const int units = rh + (dim - rot_dim);               // per head
     pdl_wait();
-    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < 2 * width; idx += gridDim.y * blockDim.x) {
-        const int which = idx >= width;                       // 0: q, 1: k
-        const int c = idx - which * width, e = c % dim;
-        const T* row = src + (size_t)t * row_stride + (which ? k_col : q_col);
-        float x = Cvt<T>::to_f32(row[c]);
-        if (e < rot_dim) {
-            const bool first = e < rh;
-            const int i = first ? e : e - rh;
-            const float y = Cvt<T>::to_f32(row[first ? c + rh : c - rh]);
-            float s, cs;
-            sincosf((float)pos * inv_freq[i], &s, &cs);
-            x = first ? x * cs - y * s : x * cs + y * s;
+    const T* qrow = src + (size_t)t * row_stride + q_col;
+    const T* krow = src + (size_t)t * row_stride + k_col;
+    float* qo = qk + (size_t)t * width;
+    float* ko = qk + (size_t)T_ * width + (size_t)t * width;
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < heads * units; idx += gridDim.y * blockDim.x) {
+        const int h = idx / units, u = idx - h * units;
+        if (u < rh) {
+            const int c0 = h * dim + u, c1 = c0 + rh;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[u], &sn, &cs);
+            const float q0 = Cvt<T>::to_f32(qrow[c0]), q1 = Cvt<T>::to_f32(qrow[c1]);
+            const float k0 = Cvt<T>::to_f32(krow[c0]), k1 = Cvt<T>::to_f32(krow[c1]);
+            qo[c0] = q0 * cs - q1 * sn;
+            qo[c1] = q1 * cs + q0 * sn;
+            ko[c0] = (k0 * cs - k1 * sn) * k_scale;
+            ko[c1] = (k1 * cs + k0 * sn) * k_scale;
+        } else {
+            const int c = h * dim + rot_dim + (u - rh);
+            qo[c] = Cvt<T>::to_f32(qrow[c]);
+            ko[c] = Cvt<T>::to_f32(krow[c]) * k_scale;
         }
-        if (which) x *= k_scale;
-        qk[(size_t)which * T_ * width + (size_t)t * width + c] = x;
     }
 }
 
@@ -380,7 +389,7 @@ static int launch_prepare(const void* src, int row_stride, int q_col, int k_col,
     if (T_ <= 0) return 0;
     if (rot_dim < 0 || rot_dim % 2 || rot_dim > dim) return RF_ERR_BAD_ARG;
     // few tokens: a row's elements over several blocks, so that the sines and cosines of a row do not queue in one
-    int by = T_ >= 512 ? 1 : (2 * heads * dim + 255) / 256;
+    int by = T_ >= 512 ? 1 : (heads * dim + 255) / 256;
     if (by > 64) by = 64;
     rf_launch(retention_prepare_kernel<T>, dim3(T_, by), dim3(256), 0, st, reinterpret_cast<const T*>(src), row_stride, q_col, k_col,
               qk, heads, dim, rot_dim, inv_freq, tok_pos, k_scale, T_);
