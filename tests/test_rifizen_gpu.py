@@ -468,13 +468,14 @@ def test_grouped_tensor_core_products_against_the_cuda_core_ones(T, E, top, H, F
     tc.check_status(dev)
 
 
+@pytest.mark.parametrize("window", [1, 7, 40, 100, 1000])
 @pytest.mark.parametrize("hd", [64, 128])
-def test_tensor_core_prompt_attention_with_cap_and_slopes(hd):
-    """bfloat16 prompts of two sequences (one continuing a cached context) with capped scores, distance slopes and a
-    window of 100: the tcgen05 kernel against the generic one."""
+def test_tensor_core_prompt_attention_with_cap_and_slopes(hd, window):
+    """bfloat16 prompts of two sequences (one continuing a cached context) with capped scores, distance slopes and windows
+    from one key to more than the prompt: the tcgen05 kernel against the generic one."""
     from rocmforge_b200 import kernels
     torch.manual_seed(hd)
-    dev, nh, nkv, window, cap, scale = "cuda", 4, 2, 100, 6.0, 0.4
+    dev, nh, nkv, cap, scale = "cuda", 4, 2, 6.0, 0.4
     lens, starts = [300, 150], [0, 70]
     T = sum(lens)
     total = [s + n for s, n in zip(starts, lens)]
@@ -530,13 +531,14 @@ def test_chunked_retention_against_the_token_by_token_kernel(dim, vdim, heads):
     assert torch.equal(s_chunk[2], state0[2]) and torch.equal(s_chunk[5], state0[5])        # slots of no sequence of the step
 
 
+@pytest.mark.parametrize("window", [1, 40, 300])
 @pytest.mark.parametrize("hd,nh,nkv", [(64, 8, 2), (128, 4, 4), (128, 6, 1)])
-def test_clustered_decode_attention_with_cap_and_slopes(hd, nh, nkv):
-    """bfloat16, one new token per sequence at contexts of 1 to 700 with a window of 300, capped scores and distance
-    slopes: the clustered kernel (1, 2 and 4 CTAs a pair) against the generic one."""
+def test_clustered_decode_attention_with_cap_and_slopes(hd, nh, nkv, window):
+    """bfloat16, one new token per sequence at contexts of 1 to 700 with windows of 1, 40 and 300, capped scores and
+    distance slopes: the clustered kernel (1, 2 and 4 CTAs a pair) against the generic one."""
     from rocmforge_b200 import kernels
     torch.manual_seed(hd + nh)
-    dev, window, cap, scale = "cuda", 300, 6.0, 0.4
+    dev, cap, scale = "cuda", 6.0, 0.4
     ctx_len = [1, 63, 64, 65, 299, 300, 301, 700]
     B = len(ctx_len)
     n_pages = [(t + 63) // 64 for t in ctx_len]
@@ -558,3 +560,28 @@ def test_clustered_decode_attention_with_cap_and_slopes(hd, nh, nkv):
                                              softcap=cap, slopes=slopes)
         assert (got.float() - want.float()).abs().max() < 3e-2, f"{splits} CTAs a pair"
     kernels.tensor_core.check_status(dev)
+
+
+def test_command_line_generates_with_this_design(folders):
+    """bin/rocmforge on a Rifizen folder: greedy tokens as the plain model picks them, sampled tokens with top-p, and the
+    statistics; the same flags as for any other model."""
+    import subprocess
+    import sys
+    from helpers import ROOT
+    name = "RA"
+    prompt = random_tokens(vocab(name), 9, 81)
+    exe = [sys.executable, os.path.join(ROOT, "bin", "rocmforge"), "--model", folders(name, "float32"), "--dtype", "float32"]
+    out = subprocess.run(exe + ["--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "6", "--temperature", "0",
+                                "--stop-ids", "", "--debug"], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    got = [int(l.split("token_id=")[1]) for l in out.stderr.splitlines() if l.startswith("[Generated]")]
+    seq = list(prompt)
+    for tok in got:
+        assert tok == int(torch.argmax(plain_logits(folders, name, "float32", seq)[-1]))
+        seq.append(tok)
+    assert len(got) == 6 and "ended by max_tokens" in out.stderr
+    js = subprocess.run(exe + ["--prompt-len", "70", "--prompt-len", "3", "--max-tokens", "5", "--temperature", "0.8", "--top-p", "0.9",
+                               "--stop-ids", "", "--stats-json", "-"], capture_output=True, text=True)
+    assert js.returncode == 0, js.stderr
+    stats = json.loads(js.stdout.strip().splitlines()[-1])
+    assert stats["prompt_tokens"] == 73 and stats["generated_tokens"] == 10
