@@ -2,7 +2,6 @@
 decoding, portions, ragged batches, slots and pages used again, generation through the public entry point, and the
 replay program; then each new kernel alone against the arithmetic written out in torch."""
 import json
-import math
 import os
 
 import numpy as np
@@ -54,13 +53,10 @@ def close(got, ref, dtype, what):
     d = got - ref
     d = d - d.mean(dim=-1, keepdim=True)
     err = d.pow(2).mean(dim=-1).sqrt() / (ref - ref.mean(dim=-1, keepdim=True)).pow(2).mean().sqrt()
-    BF16_ERRORS.append(err)
     ok = float(err.mean()) < 0.045 and float((err < 0.06).double().mean()) >= 0.9
     assert ok or err.numel() < 10 and float(err.max()) < 0.40, \
         f"{what}: row errors up to {float(err.max()):.3f}, mean {float(err.mean()):.3f}, {int((err >= 0.06).sum())} of {err.numel()} over 6 %"
 
-
-BF16_ERRORS = []
 
 
 def vocab(name):
