@@ -9,14 +9,28 @@ import torch
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values of every position (window None) or of the last ``window`` positions."""
+    """Keys and values of every position (window and chunk None), of the last ``window`` positions, or of the chunk of
+    ``chunk`` positions that the newest position lies in (chunks counted from position 0)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None      # size of a value head where it differs from a key head's
+    chunk: Optional[int] = None
+
+    def __post_init__(self):
+        if self.window and self.chunk:
+            raise ValueError("a cache request keeps a window or a chunk, not both")
 
     def group_key(self):
-        return ("kv", self.n_kv_heads, self.head_dim, self.window, self.v_head_dim)
+        return ("kv", self.n_kv_heads, self.head_dim, self.window, self.v_head_dim, self.chunk)
+
+    def first_needed(self, position: int) -> int:
+        """The first key position that a query at ``position`` (and therefore any later one) can see."""
+        if self.window:
+            return max(position - self.window + 1, 0)
+        if self.chunk:
+            return position // self.chunk * self.chunk
+        return 0
 
 
 @dataclass(frozen=True)

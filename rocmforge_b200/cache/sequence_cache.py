@@ -5,9 +5,9 @@ maeddesg/ROCmForge keeps one K and one V buffer of ``max_seq`` rows per layer fo
 sequence (src/gpu/cache.rs:23-83).  Here a sequence holds a *slot*; the slot owns pages of
 64 positions, taken from a pool when the sequence grows and given back when it ends, so
 the pool is sized by the tokens that live sequences hold together.  Layers whose needs
-differ (all keys / a window of them / other head counts) form groups with storage, pool
-and block table of their own; a group with a window drops the pages that have fallen
-out of every future query's window.  Mixers that ask for a ``StateRequest`` get tensors
+differ (all keys / a window of them / the newest chunk / other head counts) form groups with storage, pool
+and block table of their own; a group with a window or with chunks drops the pages that
+have fallen out of every future query's sight.  Mixers that ask for a ``StateRequest`` get tensors
 indexed by slot, zeroed when the slot is handed out.
 """
 from __future__ import annotations
@@ -39,6 +39,8 @@ class KVGroup:
         self.n_pages = n_pages
         self.max_pages_per_seq = max_pages_per_seq
         self.window = request.window
+        self.chunk = request.chunk
+        self.drops = bool(request.window or request.chunk)     # pages fall out of every future query's sight
         self.pool = FreeList(n_pages, "cache page")
         # [owner, k|v, page, kv_head, position in page, head_dim]; values of another head size than keys have a tensor
         # of their own (storage then holds the keys alone)
@@ -56,15 +58,14 @@ class KVGroup:
     # --- pages of one slot
     def first_needed_page(self, length_after: int) -> int:
         """Lowest logical page any query at position >= length_after - 1 ... can still see."""
-        if self.window is None:
+        if not self.drops:
             return 0
-        # the next query (position length_after) sees keys >= length_after - window + 1
-        lo = length_after - self.window + 1
-        return max(lo, 0) // PAGE
+        # the next query (position length_after) sees keys >= length_after - window + 1, or its chunk's first
+        return self.request.first_needed(length_after) // PAGE
 
     def pages_missing(self, slot: int, start: int, end: int) -> int:
         """Pages to be taken so that positions [start, end) can be written and read."""
-        lo = 0 if self.window is None else max(start - self.window + 1, 0)
+        lo = self.request.first_needed(start)
         need = 0
         for p in range(lo // PAGE, pages_for(end)):
             if self.table[slot, p] < 0:
@@ -81,8 +82,8 @@ class KVGroup:
                 self._mark(slot, p)
 
     def trim(self, slot: int, length: int) -> None:
-        """Give back pages no future query of this slot can see (window groups only)."""
-        if self.window is None:
+        """Give back pages no future query of this slot can see (groups with a window or chunks only)."""
+        if not self.drops:
             return
         keep_from = self.first_needed_page(length)
         row = self.table[slot]

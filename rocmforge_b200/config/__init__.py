@@ -3,3 +3,5 @@ from .registry import (register_architecture, architecture_for, known_architectu
                        load_config, read_config_json, architecture_name)
 from .qwen2 import Qwen2Config
 from .rifizen import RifizenConfig
+from .vilulorn import VilulornConfig
+from . import vilulorn   # (its builder registers "Vilulorn")

@@ -69,4 +69,21 @@ def load_config(folder_or_file: str):
     """config.json -> (Architecture, typed configuration)."""
     raw = read_config_json(folder_or_file)
     arch = architecture_for(architecture_name(raw))
+    if getattr(arch.config_cls, "SHAPES_FROM_TENSORS", False):
+        # a design some of whose sizes are no key of config.json but the shape of a tensor
+        return arch, arch.config_cls.from_dict(raw, shapes=tensor_shapes(folder_or_file))
     return arch, arch.config_cls.from_dict(raw)
+
+
+def tensor_shapes(folder_or_file: str):
+    """{tensor name: shape} from the headers of the folder's safetensors files (no tensor is read); None where there
+    are no such files (a configuration on its own)."""
+    from ..weights.safetensors_io import ModelFiles, SafetensorsError
+    folder = folder_or_file if os.path.isdir(folder_or_file) else os.path.dirname(os.path.abspath(folder_or_file))
+    if not (os.path.exists(os.path.join(folder, "model.safetensors"))
+            or os.path.exists(os.path.join(folder, "model.safetensors.index.json"))):
+        return None
+    try:
+        return {name: tuple(e.shape) for name, e in ModelFiles(folder).entries.items()}
+    except SafetensorsError:
+        return None                                   # the loader reports a broken file with its own message

@@ -51,7 +51,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int pos = tok_pos[b];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = rf_first_key(pos, window);
     const int c_lo = lo / DEC_CHUNK, c_hi = pos / DEC_CHUNK;
     if (c_hi >= max_chunks) {           // the launch has no CTA for the sequence's last chunk: say so, touch nothing
         if (c == 0 && tid == 0 && status) atomicExch(status, 3);
@@ -359,7 +359,7 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
     const int lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
     const int rank = splits > 1 ? (int)dcl_cluster_rank() : 0;
     const int pos = tok_pos[b];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = rf_first_key(pos, window);
     // designs that cap their scores (softcap * tanh(score / softcap)) and lower them by slope * distance afterwards
     const bool shaped = softcap > 0.f || slopes != nullptr;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;

@@ -57,7 +57,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int pos = tok_pos[t];
     const int slot = seq_slot[tok_seq[t]];
     const int* bt = block_table + (size_t)slot * max_pages;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = rf_first_key(pos, window);
 
     // rows of whole 4-element groups: 16-byte (8-byte) loads
     auto load_chunk = [&](const T* __restrict__ pages, int c0, int cnt, int hd, int ldk) {

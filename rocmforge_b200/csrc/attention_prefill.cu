@@ -74,7 +74,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     const int row_base = cu_q[seq] + q0;                // first packed token row of the tile
     int rows_here = n_new - q0; if (rows_here > PF_BM) rows_here = PF_BM;
     const int pos_first = start + q0, pos_last = start + q0 + rows_here - 1, seq_last = start + n_new - 1;
-    const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int lo_first = rf_first_key(pos_first, window);
     const int kt_lo = lo_first / RF_PAGE, kt_hi = pos_last / RF_PAGE;
     const int n_kt = kt_hi - kt_lo + 1;
 
@@ -119,8 +119,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         qa[ks][3] = r1 < rows_here ? *reinterpret_cast<const uint32_t*>(p1 + 8) : 0u;
     }
     const int pos0 = pos_first + r0, pos1 = pos_first + r1;
-    const int lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0;
+    const int lo0 = rf_first_key(pos0, window);
+    const int lo1 = rf_first_key(pos1, window);
 
     float oc[HD / 8][4];
 #pragma unroll
@@ -192,7 +192,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         const float sl2 = scale * 1.4426950408889634f;
         // a page wholly inside every row's range of this warp (below the diagonal, inside the window) needs no mask
         const bool no_mask = warp_needed && key0 + RF_PAGE - 1 <= pos_first + warp * 16 && warp * 16 + 15 < rows_here &&
-                             (window <= 0 || key0 >= pos_first + warp * 16 + 15 - window + 1);
+                             key0 >= rf_first_key(pos_first + warp * 16 + 15, window);
         float mx0 = -INFINITY, mx1 = -INFINITY;
         if (no_mask) {
 #pragma unroll

@@ -128,7 +128,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int row_base = cu_q[seq] + q0;
     int rows_here = n_new - q0; if (rows_here > AT_BM) rows_here = AT_BM;
     const int pos_first = start + q0, pos_last = pos_first + rows_here - 1, seq_last = start + n_new - 1;
-    const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const int lo_first = rf_first_key(pos_first, window);
     const int kt_lo = lo_first / AT_BN, kt_hi = pos_last / AT_BN;      // AT_BN == RF_PAGE: a tile is a page
     const int n_kt = kt_hi - kt_lo + 1;
 
@@ -223,7 +223,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const int pos_i = pos_first + row;
-        const int lo_i = (window > 0 && pos_i - window + 1 > 0) ? pos_i - window + 1 : 0;
+        const int lo_i = rf_first_key(pos_i, window);
         const bool row_ok = row < rows_here;
         // designs that cap their scores (softcap * tanh(score / softcap)) and lower them by slope * distance: the row of
         // scores is transformed in registers before the softmax (32-bit), and the exponent's factor is log2 e alone
@@ -254,7 +254,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
             }
             const bool no_mask = key0 + AT_BN - 1 <= pos_first && rows_here == AT_BM &&
-                                 (window <= 0 || key0 >= pos_last - window + 1);
+                                 key0 >= rf_first_key(pos_last, window);
             // the row of S, once, into registers (raw products; masked ones -inf).  Maximum and sum are kept
             // in four independent partial results each: one warp per scheduler cannot hide a chain of 64
             // dependent operations

@@ -33,6 +33,7 @@ MODULES: Dict[str, List[str]] = {
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "retention": ["retention.cu", "common.cuh"],
+    "gla": ["gla.cu", "common.cuh"],
     "moe": ["moe.cu", "common.cuh"],
     "random_fill": ["random_fill.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05_common.cuh", "common.cuh"],

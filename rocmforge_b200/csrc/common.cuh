@@ -6,6 +6,16 @@
 
 #define RF_PAGE 64            // tokens per cache page; the Python cache uses the same number
 
+// The first key position that a query at position pos sees; it always sees up to pos itself.  The attention kernels
+// take the rule as one number: span > 0, the last span positions (a sliding window); span < 0, the positions of the
+// query's own chunk of -span positions, chunks counted from position 0 of the sequence; 0, every position.  The bound
+// never falls as pos grows.
+__host__ __device__ __forceinline__ int rf_first_key(int pos, int span) {
+    if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+    if (span < 0) return pos / (-span) * (-span);
+    return 0;
+}
+
 // Every exported launcher returns 0, a cudaError_t (> 0) or one of these (< 0).
 #define RF_ERR_BAD_ARG (-1)
 #define RF_ERR_UNSUPPORTED (-2)

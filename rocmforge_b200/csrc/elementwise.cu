@@ -35,9 +35,12 @@ template <> struct Four<__nv_bfloat16> {
 
 // ---------------------------------------------------------------- embedding
 // out[t, :] = table[ids[t], :] widened to 32-bit (the residual stream).
+// With pos_table (a learned vector per position, [P, H]) row tok_pos[t] of it is added, in 32-bit; with rounded, the
+// stream's row is also left there in the table's dtype (for sub-layers that read the stream itself).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int H, int V) {
+                             float* __restrict__ out, int H, int V, const T* __restrict__ pos_table,
+                             const int* __restrict__ tok_pos, int P, T* __restrict__ rounded) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -45,6 +48,17 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; never read outside
     const T* row = table + (size_t)id * H;
     float* o = out + (size_t)t * H;
+    if (pos_table != nullptr || rounded != nullptr) {
+        int ps = pos_table != nullptr ? tok_pos[t] : 0;
+        ps = ps < 0 ? 0 : (ps >= P ? P - 1 : ps);       // the cache refuses sequences longer than the table
+        const T* prow = pos_table != nullptr ? pos_table + (size_t)ps * H : nullptr;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = Cvt<T>::to_f32(row[i]) + (prow != nullptr ? Cvt<T>::to_f32(prow[i]) : 0.f);
+            o[i] = v;
+            if (rounded != nullptr) rounded[(size_t)t * H + i] = Cvt<T>::from_f32(v);
+        }
+        return;
+    }
     // four elements per access where rows allow it: a decode step starts with this kernel, and 14 rounds of 2-byte
     // loads from a table row that lies in DRAM took 10 us
     if (H % 4 == 0 && (reinterpret_cast<uintptr_t>(table) % (4 * sizeof(T))) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
@@ -488,7 +502,8 @@ __global__ void add_row_kernel(float* __restrict__ h, const T* __restrict__ vec,
 //   m = a0                                            (one branch), or
 //   m = (rms(a0) * w0 + rms(a1) * w1) / 2             (two branches side by side, each normed with its own weight)
 //   h += rms(m) * w_post (+ extra)                    (extra: a row vector that the schedule adds before the next layer)
-//   y_next = rms(h) * w_next in the compute dtype     (the norm that reads the stream next, if the caller knows it)
+//   y_next = rms(h) * w_next in the compute dtype     (the norm that reads the stream next, if the caller knows it;
+//                                                      y_next without w_next: h itself, rounded to the compute dtype)
 // with rms(x) = x / sqrt(mean(x^2) + eps).  A branch comes as n0 (n1) partial sums [n][rows][H] of a K-split product,
 // added here in index order.  A block per row; the rows stay in shared memory between the passes.
 template <typename T>
@@ -539,6 +554,10 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int 
         sh += v * v;
     }
     if (y_next == nullptr) return;
+    if (w_next == nullptr) {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) y_next[base + c] = Cvt<T>::from_f32(row[c]);
+        return;
+    }
     const float rh = rsqrtf(block_sum(sh, red) * invH + eps);
     for (int c = threadIdx.x; c < H; c += blockDim.x)
         y_next[base + c] = Cvt<T>::from_f32(row[c] * rh * load_vec(w_next, w_is_f32, c));
@@ -547,7 +566,8 @@ branch_norm_add_kernel(float* __restrict__ h, const float* __restrict__ a0, int 
 // ---------------------------------------------------------------- per-head unit norm + rotation + cache write
 // A warp per head of a token's q | k | v row: q heads and k heads have hd elements, v heads hdv.  The row comes in
 // the compute dtype or as n_partials 32-bit partial sums.  With unit_norm every q and k head is divided by its root
-// mean square (x / sqrt(mean(x^2) + eps), no weight, 32-bit); then the first rot_dim elements turn as in the kernel
+// mean square (x / sqrt(mean(x^2) + eps), 32-bit) and, if q_norm_w / k_norm_w are given ([hd], one weight vector for
+// all query heads and one for all key heads), multiplied by it; then the first rot_dim elements turn as in the kernel
 // above (rot_dim 0: none); q goes to q_out, k and v into the page of (slot, position).  Key pages are
 // [n_pages, nkv, RF_PAGE, hd], value pages [n_pages, nkv, RF_PAGE, hdv].
 template <typename T, bool PARTIALS>
@@ -557,7 +577,8 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
                           const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
                           const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                           const int* __restrict__ block_table, int max_pages, T* __restrict__ k_pages,
-                          T* __restrict__ v_pages, int write_kv, int rot_dim, int interleaved, int unit_norm, float eps) {
+                          T* __restrict__ v_pages, int write_kv, int rot_dim, int interleaved, int unit_norm, float eps,
+                          const void* __restrict__ q_norm_w, const void* __restrict__ k_norm_w, int norm_w_is_f32) {
     extern __shared__ float heads_buf[];            // [warps][max(hd, hdv)]
     pdl_trigger();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -589,7 +610,12 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
         }
         float r = 1.f;
         if (unit_norm && !is_v) r = rsqrtf(warp_sum(ss) / (float)n + eps);
+        const void* nw = (unit_norm && !is_v) ? (head < nh ? q_norm_w : k_norm_w) : nullptr;
         __syncwarp();
+        if (nw != nullptr) {                              // the weighted norm comes before the rotation
+            for (int e = lane; e < n; e += 32) buf[e] *= load_vec(nw, norm_w_is_f32, e);
+            __syncwarp();
+        }
         T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
                : !is_v ? k_pages + ((size_t)page * nkv + (head - nh)) * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd
                        : v_pages + ((size_t)page * nkv + (head - nh - nkv)) * RF_PAGE * hdv + (size_t)(pos % RF_PAGE) * hdv;
@@ -610,11 +636,88 @@ head_norm_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_pa
     }
 }
 
+// ---------------------------------------------------------------- gated unit with clamped halves
+// a[t, j] = g sigmoid(alpha g) (u + 1) with g = min(gu[t, 2j], limit), u = clamp(gu[t, 2j+1], -limit, limit), evaluated in
+// 32-bit.  row_scale (float [T], may be null) multiplies both halves of row t first: W (s x) = s (W x), so an input that
+// is scaled by a routing score can be given as the unscaled product and the score.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ a, size_t n_out, int I, float limit, float alpha,
+                                   const float* __restrict__ row_scale) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_out; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, j = idx - t * I;
+        const float sc = row_scale != nullptr ? row_scale[t] : 1.f;
+        const float g = fminf(Cvt<T>::to_f32(gu[t * 2 * I + 2 * j]) * sc, limit);
+        const float u = fminf(fmaxf(Cvt<T>::to_f32(gu[t * 2 * I + 2 * j + 1]) * sc, -limit), limit);
+        a[idx] = Cvt<T>::from_f32(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    }
+}
+
+// ---------------------------------------------------------------- out[t, c] = x[t, c] * sigmoid(gate[t, c])
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ gate, int gate_stride,
+                                    T* __restrict__ out, size_t n, int W) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / W, c = idx - t * W;
+        const float g = Cvt<T>::to_f32(gate[t * gate_stride + c]);
+        out[idx] = Cvt<T>::from_f32(Cvt<T>::to_f32(x[t * x_stride + c]) / (1.f + expf(-g)));
+    }
+}
+
+// ---------------------------------------------------------------- the 32-bit stream rounded to the compute dtype
+template <typename T>
+__global__ void round_rows_kernel(const float* __restrict__ h, T* __restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = Cvt<T>::from_f32(h[idx]);
+}
+
 // ---------------------------------------------------------------- launchers
 template <typename T>
-static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
+static int launch_clamped_glu(const void* gu, void* a, int T_, int I, float limit, float alpha, const float* row_scale,
+                              cudaStream_t st) {
+    const size_t n = (size_t)T_ * I;
+    if (n == 0) return 0;
+    const size_t blocks = (n + 255) / 256;
+    rf_launch(clamped_glu_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st,
+              reinterpret_cast<const T*>(gu), reinterpret_cast<T*>(a), n, I, limit, alpha, row_scale);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_sigmoid_gate(const void* x, int x_stride, const void* gate, int gate_stride, void* out, int T_, int W,
+                               cudaStream_t st) {
+    const size_t n = (size_t)T_ * W;
+    if (n == 0) return 0;
+    const size_t blocks = (n + 255) / 256;
+    rf_launch(sigmoid_gate_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st,
+              reinterpret_cast<const T*>(x), x_stride, reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), n, W);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_round_rows(const float* h, void* out, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    rf_launch(round_rows_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st, h,
+              reinterpret_cast<T*>(out), (size_t)n);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st,
+                        const void* pos_table = nullptr, const int* tok_pos = nullptr, int P = 0, void* rounded = nullptr) {
     if (T_ <= 0) return 0;
-    rf_launch(embed_kernel<T>, dim3(T_), dim3(256), 0, st, reinterpret_cast<const T*>(table), ids, out, H, V);
+    if (pos_table != nullptr && (tok_pos == nullptr || P <= 0)) return RF_ERR_BAD_ARG;
+    rf_launch(embed_kernel<T>, dim3(T_), dim3(256), 0, st, reinterpret_cast<const T*>(table), ids, out, H, V,
+              reinterpret_cast<const T*>(pos_table), tok_pos, P, reinterpret_cast<T*>(rounded));
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -771,7 +874,8 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
                                      int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq,
                                      const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
                                      int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, int rot_dim,
-                                     int interleaved, int unit_norm, float eps, cudaStream_t st) {
+                                     int interleaved, int unit_norm, float eps, cudaStream_t st,
+                                     const void* q_norm_w = nullptr, const void* k_norm_w = nullptr, int norm_w_is_f32 = 0) {
     if (T_ <= 0) return 0;
     if (rot_dim % 2 || rot_dim < 0 || rot_dim > hd || hd <= 0 || hdv <= 0) return RF_ERR_BAD_ARG;
     const size_t smem = (size_t)4 * (hd > hdv ? hd : hdv) * sizeof(float);
@@ -783,11 +887,13 @@ static int launch_head_norm_kv_write(const void* src, int row_stride, int n_part
     if (n_partials > 0)
         rf_launch(head_norm_kv_write_kernel<T, true>, dim3(T_, by), dim3(128), smem, st, src, row_stride, n_partials, partial_stride,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
-                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
+                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
+                  q_norm_w, k_norm_w, norm_w_is_f32);
     else
         rf_launch(head_norm_kv_write_kernel<T, false>, dim3(T_, by), dim3(128), smem, st, src, row_stride, 0, (size_t)0,
                   reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
-                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps);
+                  max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim, interleaved, unit_norm, eps,
+                  q_norm_w, k_norm_w, norm_w_is_f32);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -797,6 +903,13 @@ extern "C" {
 int rf_embed(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
     return dtype == 0 ? launch_embed<float>(table, ids, out, T_, H, V, st)
                       : launch_embed<__nv_bfloat16>(table, ids, out, T_, H, V, st);
+}
+// The same with a learned position table [P, H] (row tok_pos[t] is added; null: none) and a copy of the result in the
+// table's dtype (rounded; null: none).
+int rf_embed_pos(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, const void* pos_table,
+                 const int* tok_pos, int P, void* rounded, cudaStream_t st) {
+    return dtype == 0 ? launch_embed<float>(table, ids, out, T_, H, V, st, pos_table, tok_pos, P, rounded)
+                      : launch_embed<__nv_bfloat16>(table, ids, out, T_, H, V, st, pos_table, tok_pos, P, rounded);
 }
 int rf_add_rmsnorm(int dtype, float* h, const void* pending, int kind, int n_pending, long long pstride,
                    const void* w, int w_is_f32, float eps, void* y, const int* rows, int n_rows, int H,
@@ -850,5 +963,34 @@ int rf_head_norm_kv_write(int dtype, const void* src, int row_stride, int n_part
                                                    nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
                                                    max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
                                                    unit_norm, eps, st);
+}
+// The same with weights of the q and k norms (each [hd], shared by the heads; null: a plain division).
+int rf_head_norm_kv_write_w(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride, void* q_out,
+                            int q_out_stride, int nh, int nkv, int hd, int hdv, const float* inv_freq, const int* tok_seq,
+                            const int* tok_pos, const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
+                            void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, int unit_norm, float eps,
+                            const void* q_norm_w, const void* k_norm_w, int norm_w_is_f32, cudaStream_t st) {
+    return dtype == 0
+        ? launch_head_norm_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride, nh, nkv,
+                                           hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, max_pages, k_pages,
+                                           v_pages, write_kv, T_, rot_dim, interleaved, unit_norm, eps, st, q_norm_w, k_norm_w,
+                                           norm_w_is_f32)
+        : launch_head_norm_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, q_out, q_out_stride,
+                                                   nh, nkv, hd, hdv, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                                                   max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved,
+                                                   unit_norm, eps, st, q_norm_w, k_norm_w, norm_w_is_f32);
+}
+int rf_clamped_glu(int dtype, const void* gu, void* a, int T_, int I, float limit, float alpha, const float* row_scale,
+                   cudaStream_t st) {
+    return dtype == 0 ? launch_clamped_glu<float>(gu, a, T_, I, limit, alpha, row_scale, st)
+                      : launch_clamped_glu<__nv_bfloat16>(gu, a, T_, I, limit, alpha, row_scale, st);
+}
+int rf_sigmoid_gate(int dtype, const void* x, int x_stride, const void* gate, int gate_stride, void* out, int T_, int W,
+                    cudaStream_t st) {
+    return dtype == 0 ? launch_sigmoid_gate<float>(x, x_stride, gate, gate_stride, out, T_, W, st)
+                      : launch_sigmoid_gate<__nv_bfloat16>(x, x_stride, gate, gate_stride, out, T_, W, st);
+}
+int rf_round_rows(int dtype, const float* h, void* out, long long n, cudaStream_t st) {
+    return dtype == 0 ? launch_round_rows<float>(h, out, n, st) : launch_round_rows<__nv_bfloat16>(h, out, n, st);
 }
 }

@@ -2,18 +2,21 @@
 // so that one grouped product serves all experts of a step without the host ever learning the counts.
 //
 //   moe_route     per token: the `top` largest of E router logits (32-bit; of equal logits the lower index), and
-//                 the softmax over the chosen logits only
+//                 their weights: the softmax over the chosen logits only (scoring 0), or each chosen logit's own
+//                 sigmoid, not renormalised (scoring 1)
 //   moe_sort      counting sort of the T*top (token, choice) pairs by expert: perm[sorted row] = pair,
 //                 inv[pair] = sorted row, and the table of row tiles for the grouped product
 //                 (tiles[0] = number of tiles, then (expert, first row, end row) per tile; a tile never spans experts)
 //   moe_combine   out[t] = sum over the token's choices, in the order of the choices, of weight * expert output row
+//                 (no weights: the plain sum, for designs whose weights went into the experts' inputs)
+//   moe_scale_gather / moe_pair_weights   the sorted rows times their pair's weight; the weights in sorted order
 // A row of the grouped product depends on its own token alone, so where the sort puts a pair changes no bit.
 #include "common.cuh"
 
 #define MOE_MAX_TOP 16
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ idx,
-                                 float* __restrict__ w, int T_) {
+                                 float* __restrict__ w, int T_, int scoring) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -32,6 +35,13 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
         }
         chosen[k] = best;
         val[k] = bv;
+    }
+    if (scoring == 1) {
+        for (int k = 0; k < top; ++k) {
+            idx[(size_t)t * top + k] = chosen[k];
+            w[(size_t)t * top + k] = 1.f / (1.f + expf(-val[k]));
+        }
+        return;
     }
     float sum = 0.f;
     const float largest = val[0];
@@ -85,7 +95,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / H, c = i - t * H;
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc = fmaf(w[t * top + k], y[(size_t)inv[t * top + k] * H + c], acc);
+        for (int k = 0; k < top; ++k) acc = fmaf(w != nullptr ? w[t * top + k] : 1.f, y[(size_t)inv[t * top + k] * H + c], acc);
         out[i] = acc;
     }
 }
@@ -107,7 +117,46 @@ __global__ void moe_gather_kernel(const uint8_t* __restrict__ x, long long x_str
     }
 }
 
+// out[r, :] = x[perm[r] / top, :] * w[perm[r]] in the dtype of x (the product is formed in 32-bit): the input of an
+// expert whose routing weight multiplies what goes in instead of what comes out
+template <typename T>
+__global__ void moe_scale_gather_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ perm,
+                                        const float* __restrict__ w, int top, T* __restrict__ out, int K) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x, pair = perm[r];
+    const float sc = w[pair];
+    const T* src = x + (size_t)(pair / top) * x_stride;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) out[(size_t)r * K + i] = Cvt<T>::from_f32(Cvt<T>::to_f32(src[i]) * sc);
+}
+
+// ws[r] = w[perm[r]]: the pairs' weights in sorted order (a grouped product's epilogue reads them by row)
+__global__ void moe_pair_weights_kernel(const int* __restrict__ perm, const float* __restrict__ w, float* __restrict__ ws, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n) ws[r] = w[perm[r]];
+}
+
 extern "C" {
+int rf_moe_scale_gather(int dtype, const void* x, long long x_stride, const int* perm, const float* w, int top, void* out,
+                        int K, int n, cudaStream_t st) {
+    if (n <= 0 || K <= 0) return 0;
+    if (dtype == 0)
+        rf_launch(moe_scale_gather_kernel<float>, dim3(n), dim3(128), 0, st, reinterpret_cast<const float*>(x), x_stride, perm, w,
+                  top, reinterpret_cast<float*>(out), K);
+    else
+        rf_launch(moe_scale_gather_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(x),
+                  x_stride, perm, w, top, reinterpret_cast<__nv_bfloat16*>(out), K);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+int rf_moe_pair_weights(const int* perm, const float* w, float* ws, int n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    rf_launch(moe_pair_weights_kernel, dim3((n + 255) / 256), dim3(256), 0, st, perm, w, ws, n);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
 int rf_moe_gather(const void* x, long long x_stride_bytes, const int* perm, int top, void* out, int row_bytes, int n,
                   cudaStream_t st) {
     if (n <= 0 || row_bytes <= 0) return 0;
@@ -118,12 +167,20 @@ int rf_moe_gather(const void* x, long long x_stride_bytes, const int* perm, int 
     RF_LAUNCH_CHECK();
     return 0;
 }
-int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_, cudaStream_t st) {
+static int route(const float* logits, int E, int top, int* idx, float* w, int T_, int scoring, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > E) return RF_ERR_UNSUPPORTED;
-    rf_launch(moe_route_kernel, dim3((T_ + 127) / 128), dim3(128), 0, st, logits, E, top, idx, w, T_);
+    if (scoring != 0 && scoring != 1) return RF_ERR_BAD_ARG;
+    rf_launch(moe_route_kernel, dim3((T_ + 127) / 128), dim3(128), 0, st, logits, E, top, idx, w, T_, scoring);
     RF_LAUNCH_CHECK();
     return 0;
+}
+int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_, cudaStream_t st) {
+    return route(logits, E, top, idx, w, T_, 0, st);
+}
+// scoring: 0 = softmax over the chosen logits, 1 = sigmoid of each chosen logit
+int rf_moe_route_scored(const float* logits, int E, int top, int* idx, float* w, int T_, int scoring, cudaStream_t st) {
+    return route(logits, E, top, idx, w, T_, scoring, st);
 }
 int rf_moe_sort(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
                 cudaStream_t st) {

@@ -121,10 +121,11 @@ retention_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, 
     }
 }
 
-// a warp per (token, head): out = o / sqrt(mean(o^2) + eps) * silu(gate)
+// a warp per (token, head): out = o / sqrt(mean(o^2) + eps) (* w, a weight [vdim] shared by the heads, if given) * silu(gate)
 template <typename T>
 __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
-                                      T* __restrict__ out, int heads, int vdim, float eps, int T_) {
+                                      T* __restrict__ out, int heads, int vdim, float eps, int T_,
+                                      const void* __restrict__ norm_w, int w_is_f32) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -139,7 +140,8 @@ __global__ void retention_gate_kernel(const float* __restrict__ o, const T* __re
         const float r = rsqrtf(warp_sum(ss) / (float)vdim + eps);
         for (int e = lane; e < vdim; e += 32) {
             const float g = Cvt<T>::to_f32(gate[(size_t)t * gate_stride + (size_t)h * vdim + e]);
-            out[(size_t)t * heads * vdim + (size_t)h * vdim + e] = Cvt<T>::from_f32(orow[e] * r * (g / (1.f + expf(-g))));
+            const float wn = norm_w != nullptr ? load_vec(norm_w, w_is_f32, e) : 1.f;
+            out[(size_t)t * heads * vdim + (size_t)h * vdim + e] = Cvt<T>::from_f32(orow[e] * r * wn * (g / (1.f + expf(-g))));
         }
     }
 }
@@ -426,12 +428,12 @@ static int launch_scan(const float* q, const float* k, const void* v, int v_stri
 
 template <typename T>
 static int launch_gate(const float* o, const void* gate, int gate_stride, void* out, int heads, int vdim, float eps, int T_,
-                       cudaStream_t st) {
+                       cudaStream_t st, const void* w = nullptr, int w_is_f32 = 0) {
     const long long total = (long long)T_ * heads;
     if (total <= 0) return 0;
     const long long blocks = (total + 7) / 8;
     rf_launch(retention_gate_kernel<T>, dim3((unsigned)(blocks > 148 * 16 ? 148 * 16 : blocks)), dim3(256), 0, st, o,
-              reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), heads, vdim, eps, T_);
+              reinterpret_cast<const T*>(gate), gate_stride, reinterpret_cast<T*>(out), heads, vdim, eps, T_, w, w_is_f32);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -460,5 +462,11 @@ int rf_retention_gate(int dtype, const float* o, const void* gate, int gate_stri
                       int T_, cudaStream_t st) {
     return dtype == 0 ? launch_gate<float>(o, gate, gate_stride, out, heads, vdim, eps, T_, st)
                       : launch_gate<__nv_bfloat16>(o, gate, gate_stride, out, heads, vdim, eps, T_, st);
+}
+// The same with a weight [vdim] of the per-head norm, shared by the heads.
+int rf_retention_gate_w(int dtype, const float* o, const void* gate, int gate_stride, void* out, int heads, int vdim, float eps,
+                        int T_, const void* w, int w_is_f32, cudaStream_t st) {
+    return dtype == 0 ? launch_gate<float>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32)
+                      : launch_gate<__nv_bfloat16>(o, gate, gate_stride, out, heads, vdim, eps, T_, st, w, w_is_f32);
 }
 }

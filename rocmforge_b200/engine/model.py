@@ -17,6 +17,7 @@ import torch
 
 from ..cache import SequenceCache
 from ..parts.base import Block, Norm, Part
+from ..parts.block import ReadsStream
 from ..parts.embedding import OutputHead, TokenEmbedding
 from ..weights import ParamSpec, load_folder, random_tensors
 from .batch import BatchError, DeviceDescriptor, StepBatch, StepRequest
@@ -51,12 +52,16 @@ class ModelSpec:
     stop_token_ids: List[int] = field(default_factory=list)
     pass_offsets: Optional[Part] = None              # parts.offsets.PassOffsets, for schedules with pass_index
     pass_offsets_prefix: str = ""
+    positions: Optional[Part] = None                 # parts.embedding.LearnedPositions: a learned vector per position, added to the embedding
+    positions_prefix: str = ""
 
     def named_parts(self) -> Dict[str, Part]:
         """{tensor-name prefix: leaf part}."""
         out: Dict[str, Part] = {self.embedding_prefix: self.embedding}
         if self.pass_offsets is not None:
             out[self.pass_offsets_prefix] = self.pass_offsets
+        if self.positions is not None:
+            out[self.positions_prefix] = self.positions
         for prefix, block in zip(self.block_prefixes, self.blocks):
             for sub, part in block.sub_parts().items():
                 out[prefix + sub] = part
@@ -191,7 +196,16 @@ class Model:
     def forward(self, ctx: StepContext, cache: SequenceCache) -> Optional[torch.Tensor]:
         """The layers in schedule order on the batch that ``ctx`` describes."""
         spec = self.spec
-        stream = ResidualStream(spec.embedding.forward(ctx, ctx.tokens))
+        first = spec.blocks[spec.schedule[0].layer].entry_norm() if spec.schedule else None
+        if spec.positions is not None or isinstance(first, ReadsStream):
+            # the position vectors are added, and a first layer that reads the stream itself gets its rounded copy, by
+            # the embedding's kernel
+            h, y = spec.embedding.forward_with(ctx, ctx.tokens, spec.positions, rounded=isinstance(first, ReadsStream))
+            stream = ResidualStream(h)
+            if y is not None:
+                stream.prepared = (first, y)
+        else:
+            stream = ResidualStream(spec.embedding.forward(ctx, ctx.tokens))
         if spec.schedule and spec.schedule[0].pass_index is not None:
             spec.pass_offsets.add(ctx, stream, spec.schedule[0].pass_index)
         for i, entry in enumerate(spec.schedule):

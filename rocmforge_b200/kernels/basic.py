@@ -34,6 +34,66 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def embed_positions(table: torch.Tensor, ids: torch.Tensor, pos_table: torch.Tensor | None, tok_pos: torch.Tensor | None,
+                    rounded: bool = False):
+    """(h, y): h[t] = table[ids[t]] (+ pos_table[tok_pos[t]], a learned vector per position) as float32, the sum formed
+    in 32-bit; y is h in the table's dtype if ``rounded`` (for sub-layers that read the stream itself), else None."""
+    need_cuda(table, ids, pos_table, tok_pos)
+    need(table.dim() == 2 and table.is_contiguous(), "embed: table must be a contiguous matrix")
+    need(ids.dtype == torch.int32 and ids.dim() == 1, "embed: ids must be a 1-d int32 tensor")
+    V, H = table.shape
+    T = ids.shape[0]
+    P = 0
+    if pos_table is not None:
+        need(pos_table.dim() == 2 and pos_table.shape[1] == H and pos_table.is_contiguous() and pos_table.dtype == table.dtype,
+             "embed: the position table must be [positions, H] of the embedding's dtype")
+        need(tok_pos is not None and tok_pos.dtype == torch.int32 and tok_pos.shape == (T,), "embed: one int32 position per token")
+        P = pos_table.shape[0]
+    h = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    y = torch.empty((T, H), dtype=table.dtype, device=table.device) if rounded else None
+    f = _f("elementwise", "rf_embed_pos", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+           c_void_p, c_void_p)
+    check(f(dtype_code(table.dtype), ptr(table), ptr(ids), ptr(h), T, H, V, ptr(pos_table), ptr(tok_pos), P, ptr(y), stream()),
+          "embed_positions")
+    return h, y
+
+
+def round_rows(h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream rounded to ``dtype`` (a copy)."""
+    need_cuda(h)
+    need(h.dtype == torch.float32 and h.is_contiguous(), "round_rows: a contiguous float32 tensor")
+    out = torch.empty(h.shape, dtype=dtype, device=h.device)
+    f = _f("elementwise", "rf_round_rows", c_int, c_void_p, c_void_p, c_ll, c_void_p)
+    check(f(dtype_code(dtype), ptr(h), ptr(out), h.numel(), stream()), "round_rows")
+    return out
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float, row_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """a[t, j] = g sigmoid(alpha g) (u + 1) with g = min(s gu[t, 2j], limit), u = clamp(s gu[t, 2j+1], -limit, limit) and
+    s = row_scale[t] (float32 [T]; 1 without), evaluated in 32-bit."""
+    need_cuda(gu, row_scale)
+    need(gu.dim() == 2 and gu.is_contiguous() and gu.shape[1] % 2 == 0, "clamped_glu: input must be [T, 2I]")
+    T, I2 = gu.shape
+    need(row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() >= T and row_scale.is_contiguous()),
+         "clamped_glu: row_scale must be float32 [T]")
+    out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
+    f = _f("elementwise", "rf_clamped_glu", c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p)
+    check(f(dtype_code(gu.dtype), ptr(gu), ptr(out), T, I2 // 2, float(limit), float(alpha), ptr(row_scale), stream()), "clamped_glu")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x * sigmoid(gate), element by element (32-bit inside); both [T, W] views with unit inner stride."""
+    need_cuda(x, gate)
+    need(x.dim() == 2 and gate.shape == x.shape and x.stride(1) == 1 and gate.stride(1) == 1 and x.dtype == gate.dtype,
+         "sigmoid_gate: x and gate must be [T, W] of one dtype")
+    T, W = x.shape
+    out = torch.empty((T, W), dtype=x.dtype, device=x.device)
+    f = _f("elementwise", "rf_sigmoid_gate", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), x.stride(0), ptr(gate), gate.stride(0), ptr(out), T, W, stream()), "sigmoid_gate")
+    return out
+
+
 def add_rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, compute_dtype: torch.dtype,
                 pending: torch.Tensor | None = None, rows: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
@@ -194,11 +254,20 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
     return out
 
 
+def key_span(window: int | None, chunk: int | None = None) -> int:
+    """The one number by which the attention kernels know which keys a query sees (rf_first_key in csrc/common.cuh):
+    the last ``window`` positions (> 0), the positions of the query's own chunk of ``chunk`` positions, chunks counted
+    from position 0 (< 0), or all (0)."""
+    need(not (window and chunk), "attention: a window or chunks, not both")
+    return -int(chunk) if chunk else int(window or 0)
+
+
 def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                       tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                       out: torch.Tensor | None = None, *, v_head_dim: int | None = None, softcap: float | None = None,
-                      slopes: torch.Tensor | None = None) -> torch.Tensor:
-    """Attention of the T new tokens over the paged cache (their own keys included).
+                      slopes: torch.Tensor | None = None, chunk: int | None = None) -> torch.Tensor:
+    """Attention of the T new tokens over the paged cache (their own keys included).  ``window`` / ``chunk``: see
+    ``key_span``.
 
     ``v_head_dim``: size of a value head where it differs from a key head's (the output is [T, heads * v_head_dim]);
     ``softcap``: scores become softcap * tanh(score / softcap); ``slopes`` (float32 [heads]): after the cap, a score is
@@ -213,6 +282,7 @@ def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
          "attention: bad cache page shape")
     if out is None:
         out = torch.empty((T, n_heads * vd), dtype=q.dtype, device=q.device)
+    window = key_span(window, chunk)
     if vd != head_dim or softcap or slopes is not None:
         need(slopes is None or (slopes.dtype == torch.float32 and slopes.shape == (n_heads,) and slopes.is_contiguous()),
              "attention: slopes must be float32 [heads]")
@@ -221,7 +291,7 @@ def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
                c_void_p, c_int, c_int, c_void_p)
         check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
                 ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
-                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), int(window or 0), T, stream()),
+                n_kv_heads, head_dim, vd, float(scale), float(softcap or 0.0), ptr(slopes), window, T, stream()),
               f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, v_head_dim={vd})")
         return out
     f = _f("attention_generic", "rf_attention_generic", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
@@ -229,7 +299,7 @@ def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
            c_void_p)
     check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
             ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
-            n_kv_heads, head_dim, float(scale), int(window or 0), T, stream()),
+            n_kv_heads, head_dim, float(scale), window, T, stream()),
           f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
 
@@ -312,7 +382,7 @@ def attention_decode_scratch(B: int, n_heads: int, n_kv_heads: int, head_dim: in
 def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                      tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None, max_chunks: int,
                      part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
-                     out: torch.Tensor | None = None) -> torch.Tensor:
+                     out: torch.Tensor | None = None, *, chunk: int | None = None) -> torch.Tensor:
     """One new token per sequence over the bfloat16 paged cache, keys in chunks of 128.
 
     ``max_chunks`` must cover the longest sequence (ceil(length / 128)); ``part_o``, ``part_ml`` (float32)
@@ -340,7 +410,7 @@ def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
     from .tensor_core import status_word
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), ptr(tok_seq), ptr(tok_pos),
             ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale),
-            int(window or 0), B, max_chunks, ptr(part_o), ptr(part_ml), ptr(counters), ptr(status_word(q.device)),
+            key_span(window, chunk), B, max_chunks, ptr(part_o), ptr(part_ml), ptr(counters), ptr(status_word(q.device)),
             stream()),
           f"attention_decode (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
@@ -356,7 +426,7 @@ def attention_prefill_supported(n_heads: int, n_kv_heads: int, head_dim: int) ->
 
 def attention_prefill(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                       q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
-                      window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+                      window: int | None, out: torch.Tensor | None = None, *, chunk: int | None = None) -> torch.Tensor:
     """Tiled causal attention of the new tokens over the bfloat16 paged cache (head_dim 64 or 128).
 
     ``q_tiles`` is an int32 array of (sequence index, first row within the sequence's new tokens) pairs,
@@ -379,7 +449,7 @@ def attention_prefill(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
            c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
             q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
-            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
+            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), key_span(window, chunk),
             ptr(status_word(q.device)), stream()),
           f"attention_prefill (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
@@ -410,7 +480,8 @@ def decode_splits(B: int, n_kv_heads: int, longest: int | None = None, window: i
 
 
 def decode_pages(longest: int, window: int | None) -> int:
-    """Most pages of 64 positions that a new token at context length ``longest`` reads."""
+    """Most pages of 64 positions that a new token at context length ``longest`` reads (``window``: the most keys a
+    query sees, be it a sliding window or a chunk)."""
     pages = (max(1, longest) + PAGE - 1) // PAGE
     if window:
         pages = min(pages, (window + PAGE - 2) // PAGE + 1)
@@ -421,7 +492,7 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
                            tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
                            splits: int | None = None, warps: int | None = None,
                            out: torch.Tensor | None = None, *, softcap: float | None = None,
-                           slopes: torch.Tensor | None = None) -> torch.Tensor:
+                           slopes: torch.Tensor | None = None, chunk: int | None = None) -> torch.Tensor:
     """One new token per sequence over the bfloat16 paged cache: a cluster of ``splits`` CTAs per (sequence,
     kv head), every warp on its own tiles of keys; merged through distributed shared memory.  ``warps``
     per CTA: 8 while one CTA per SM is enough for the batch, else 4 (three CTAs fit an SM)."""
@@ -448,7 +519,7 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
            c_float, c_void_p, c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(tok_seq),
             ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim,
-            float(scale), int(window or 0), B, splits, warps, float(softcap or 0.0), ptr(slopes),
+            float(scale), key_span(window, chunk), B, splits, warps, float(softcap or 0.0), ptr(slopes),
             ptr(status_word(q.device)), stream()),
           f"attention_decode_warps (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
     return out
@@ -465,7 +536,7 @@ def attention_prefill_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int)
 def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
                          q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
                          window: int | None, out: torch.Tensor | None = None, *, softcap: float | None = None,
-                         slopes: torch.Tensor | None = None) -> torch.Tensor:
+                         slopes: torch.Tensor | None = None, chunk: int | None = None) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products as tcgen05.mma (accumulators in tensor
     memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles.  ``softcap`` and ``slopes`` as in
     ``attention_generic``."""
@@ -490,7 +561,7 @@ def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
            c_int, c_float, c_void_p, c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), T, ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
             q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
-            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0), float(softcap or 0.0),
+            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), key_span(window, chunk), float(softcap or 0.0),
             ptr(slopes), ptr(status_word(q.device)), stream()),
           f"attention_prefill_tc (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
@@ -517,13 +588,15 @@ def add_row(h: torch.Tensor, vec: torch.Tensor) -> None:
 
 
 def branch_norm_add(h: torch.Tensor, branches, post_weight: torch.Tensor, eps: float, compute_dtype: torch.dtype, *,
-                    extra: torch.Tensor | None = None, next_weight: torch.Tensor | None = None) -> torch.Tensor | None:
+                    extra: torch.Tensor | None = None, next_weight: torch.Tensor | None = None,
+                    next_rounded: bool = False) -> torch.Tensor | None:
     """The residual update of a block that norms its sub-layers' outputs, in 32-bit and in one pass over the rows:
 
         m = a0                                    for branches == [(a0, None)]
         m = (rms(a0) * w0 + rms(a1) * w1) / 2     for branches == [(a0, w0), (a1, w1)]
         h += rms(m) * post_weight (+ extra)
-        returns rms(h) * next_weight in the compute dtype if ``next_weight`` is given, else None
+        returns rms(h) * next_weight in the compute dtype if ``next_weight`` is given, h itself rounded to the compute
+        dtype if ``next_rounded`` (the next sub-layer reads the stream itself), else None
 
     with rms(x) = x / sqrt(mean(x^2) + eps).  A branch is float32 [T, H], or a stack [S, T, H] of partial sums of a K-split
     product, which are added here in index order; all weight vectors share one dtype.
@@ -543,7 +616,8 @@ def branch_norm_add(h: torch.Tensor, branches, post_weight: torch.Tensor, eps: f
     n1 = (a1.shape[0] if a1.dim() == 3 else 1) if a1 is not None else 0
     need(all(v.shape == (H,) and v.dtype == vecs[0].dtype and v.is_contiguous() for v in vecs)
          and vecs[0].dtype in (torch.float32, torch.bfloat16), "branch_norm_add: weight vectors must be [H] of one dtype")
-    y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if next_weight is not None else None
+    need(not (next_rounded and next_weight is not None), "branch_norm_add: the next reader takes a norm or the stream itself")
+    y = torch.empty((T, H), dtype=compute_dtype, device=h.device) if (next_weight is not None or next_rounded) else None
     f = _f("elementwise", "rf_branch_norm_add", c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p)
     check(f(dtype_code(compute_dtype), ptr(h), ptr(a0), n0, ptr(w0), ptr(a1), n1, ptr(w1), ptr(post_weight), ptr(extra),
@@ -556,23 +630,27 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                        inv_freq: torch.Tensor | None, tok_seq, tok_pos, seq_slot, block_table: torch.Tensor,
                        k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
                        compute_dtype: torch.dtype | None = None, rot_dim: int = 0, interleaved: bool = False,
-                       unit_norm_eps: float | None = None) -> torch.Tensor:
+                       unit_norm_eps: float | None = None, q_norm_weight: torch.Tensor | None = None,
+                       k_norm_weight: torch.Tensor | None = None) -> torch.Tensor:
     """q | k | v rows on their way into the cache, for heads that are normed and for values of another size than keys.
 
     ``qkv`` is [T, heads*head_dim + kv_heads*head_dim + kv_heads*v_head_dim] in the compute dtype, or a float32 stack
     [S, T, ...] of partial sums.  With ``unit_norm_eps`` every query and key head is divided by its root mean square
-    (x / sqrt(mean(x^2) + eps), no weight) in 32-bit; then the first ``rot_dim`` elements turn (0: no rotation).
+    (x / sqrt(mean(x^2) + eps)) in 32-bit and multiplied by ``q_norm_weight`` / ``k_norm_weight`` ([head_dim], shared by
+    the heads) where given; then the first ``rot_dim`` elements turn (0: no rotation).  The rows may hold more columns
+    than q | k | v (a gate's, say); without ``write_kv`` only the q heads are read.
     Returns q [T, heads*head_dim] in the compute dtype; k and v go to their pages.
     """
     need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages)
     width = (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_head_dim
     partials = qkv.dim() == 3
     if partials:
-        need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] == width and compute_dtype is not None,
+        need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] >= (width if write_kv else n_heads * head_dim) and compute_dtype is not None,
              "head_norm_kv_write: partial sums must be a contiguous float32 [S, T, width] stack, with the compute dtype named")
-        S, T, dt, row_stride, pstride = qkv.shape[0], qkv.shape[1], compute_dtype, width, qkv.shape[1] * width
+        S, T, dt, row_stride, pstride = qkv.shape[0], qkv.shape[1], compute_dtype, qkv.shape[2], qkv.shape[1] * qkv.shape[2]
     else:
-        need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == width, "head_norm_kv_write: qkv must be [T, width]")
+        need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= (width if write_kv else n_heads * head_dim),
+             "head_norm_kv_write: qkv must be [T, >= width]")
         S, T, dt, row_stride, pstride = 0, qkv.shape[0], qkv.dtype, qkv.stride(0), 0
     need(rot_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2),
          "head_norm_kv_write: inv_freq must hold rot_dim/2 float32 frequencies")
@@ -582,13 +660,19 @@ def head_norm_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
              and v_pages.is_contiguous() and tuple(v_pages.shape[1:]) == (n_kv_heads, PAGE, v_head_dim),
              "head_norm_kv_write: pages must be [n_pages, kv_heads, 64, head size] of the compute dtype")
     q_out = torch.empty((T, n_heads * head_dim), dtype=dt, device=qkv.device)
-    f = _f("elementwise", "rf_head_norm_kv_write", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
+    nws = [w for w in (q_norm_weight, k_norm_weight) if w is not None]
+    need_cuda(*nws)
+    need(all(w.shape == (head_dim,) and w.is_contiguous() and w.dtype == nws[0].dtype for w in nws)
+         and (not nws or (unit_norm_eps is not None and nws[0].dtype in (torch.float32, torch.bfloat16))),
+         "head_norm_kv_write: norm weights are [head_dim] vectors of one dtype and go with unit_norm_eps")
+    f = _f("elementwise", "rf_head_norm_kv_write_w", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_int,
            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-           c_int, c_int, c_float, c_void_p)
+           c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p)
     check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(q_out), q_out.stride(0), n_heads, n_kv_heads, head_dim,
             v_head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
             ptr(k_pages), ptr(v_pages), int(write_kv), T, int(rot_dim), int(interleaved), int(unit_norm_eps is not None),
-            float(unit_norm_eps or 0.0), stream()), "head_norm_kv_write")
+            float(unit_norm_eps or 0.0), ptr(q_norm_weight), ptr(k_norm_weight), int(bool(nws) and nws[0].dtype == torch.float32),
+            stream()), "head_norm_kv_write")
     return q_out
 
 
@@ -682,17 +766,62 @@ def retention_chunked(qk: torch.Tensor, v: torch.Tensor, state: torch.Tensor, de
     return o
 
 
-def retention_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float) -> torch.Tensor:
-    """o / sqrt(mean(o^2) + eps) per head, times silu(gate), in the gate's dtype."""
-    need_cuda(o, gate)
+def retention_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float,
+                   weight: torch.Tensor | None = None) -> torch.Tensor:
+    """o / sqrt(mean(o^2) + eps) per head (times ``weight`` [vdim], one vector for all heads, if given), times silu(gate),
+    in the gate's dtype."""
+    need_cuda(o, gate, weight)
+    need(weight is None or (weight.shape == (vdim,) and weight.is_contiguous() and weight.dtype in (torch.float32, torch.bfloat16)),
+         "retention_gate: the norm's weight must be [vdim]")
     T = o.shape[0]
     need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, heads * vdim), "retention_gate: bad o")
     need(gate.shape == (T, heads * vdim) and gate.stride(1) == 1, "retention_gate: gate must be [T, heads*vdim]")
     out = torch.empty((T, heads * vdim), dtype=gate.dtype, device=o.device)
-    f = _f("retention", "rf_retention_gate", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
-    check(f(dtype_code(gate.dtype), ptr(o), ptr(gate), gate.stride(0), ptr(out), heads, vdim, float(eps), T, stream()),
-          "retention_gate")
+    f = _f("retention", "rf_retention_gate_w", c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int,
+           c_void_p, c_int, c_void_p)
+    check(f(dtype_code(gate.dtype), ptr(o), ptr(gate), gate.stride(0), ptr(out), heads, vdim, float(eps), T, ptr(weight),
+            int(weight is not None and weight.dtype == torch.float32), stream()), "retention_gate")
     return out
+
+
+# ---------------------------------------------------------------- gated linear attention (csrc/gla.cu)
+
+def gla_prepare(proj: torch.Tensor, q_col: int, k_col: int, z: torch.Tensor, heads: int, dim: int, q_scale: float,
+                tau: float) -> torch.Tensor:
+    """float32 [3, T, heads*dim]: q of the projection's rows (columns q_col..) times ``q_scale``, k (columns k_col..), and
+    the decay alpha = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau) per key channel, from z float32 [T, heads*dim]."""
+    need_cuda(proj, z)
+    T, width = proj.shape[0], heads * dim
+    need(proj.dim() == 2 and proj.stride(1) == 1 and max(q_col, k_col) + width <= proj.shape[1],
+         "gla_prepare: the projection must be [T, columns] and hold q and k")
+    need(z.dtype == torch.float32 and z.shape == (T, width) and z.is_contiguous(), "gla_prepare: z must be float32 [T, heads*dim]")
+    qka = torch.empty((3, T, width), dtype=torch.float32, device=proj.device)
+    f = _f("gla", "rf_gla_prepare", c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int,
+           c_void_p)
+    check(f(dtype_code(proj.dtype), ptr(proj), proj.stride(0), q_col, k_col, ptr(z), ptr(qka), width, float(q_scale), float(tau),
+            T, stream()), "gla_prepare")
+    return qka
+
+
+def gla_scan(qka: torch.Tensor, v: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor,
+             heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t, token by token for every sequence of the step; ``qka`` as
+    ``gla_prepare`` leaves it; ``state`` [slots, heads, vdim, dim] float32 (S transposed) is read at the step's start and
+    left as after its last token; ``v`` a [T, heads*vdim] view (rows may be strided).  Returns o float32 [T, heads*vdim]."""
+    need_cuda(qka, v, state, cu_q, seq_slot)
+    T = qka.shape[1]
+    need(qka.dtype == torch.float32 and qka.is_contiguous() and qka.shape == (3, T, heads * dim), "gla_scan: bad q/k/alpha")
+    need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "gla_scan: v must be [T, heads*vdim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
+         "gla_scan: state must be float32 [slots, heads, vdim, dim]")
+    B = seq_slot.shape[0]
+    o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qka.device)
+    f = _f("gla", "rf_gla_scan", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_int, c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(v.dtype), ptr(qka[0]), ptr(qka[1]), ptr(qka[2]), ptr(v), v.stride(0), ptr(state), ptr(o), ptr(cu_q),
+            ptr(seq_slot), B, heads, dim, vdim, device_sm_count(qka.device), stream()),
+          f"gla_scan (heads={heads}, dim={dim}, vdim={vdim})")
+    return o
 
 
 # ---------------------------------------------------------------- routing of experts (csrc/moe.cu)
@@ -712,17 +841,47 @@ def moe_gather(x: torch.Tensor, perm: torch.Tensor, top: int) -> torch.Tensor:
     return out
 
 
-def moe_route(logits: torch.Tensor, top: int):
+MOE_SCORINGS = {"softmax_of_chosen": 0, "sigmoid": 1}
+
+
+def moe_route(logits: torch.Tensor, top: int, scoring: str = "softmax_of_chosen"):
     """(experts int32 [T, top], weights float32 [T, top]): the ``top`` largest router logits of every token (of equal
-    logits the lower index) and the softmax over those alone."""
+    logits the lower index) and their weights: the softmax over those alone, or (``scoring`` "sigmoid") each one's
+    own sigmoid, not renormalised."""
+    need(scoring in MOE_SCORINGS, f"moe_route: scoring {scoring!r} is not one of {sorted(MOE_SCORINGS)}")
     need_cuda(logits)
     need(logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous(), "moe_route: logits must be float32 [T, E]")
     T, E = logits.shape
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    f = _f("moe", "rf_moe_route", c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p)
-    check(f(ptr(logits), E, top, ptr(idx), ptr(w), T, stream()), f"moe_route (E={E}, top={top})")
+    f = _f("moe", "rf_moe_route_scored", c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(ptr(logits), E, top, ptr(idx), ptr(w), T, MOE_SCORINGS[scoring], stream()), f"moe_route (E={E}, top={top})")
     return idx, w
+
+
+def moe_scale_gather(x: torch.Tensor, perm: torch.Tensor, w: torch.Tensor, top: int) -> torch.Tensor:
+    """out[r] = x[perm[r] // top] * w.flat[perm[r]] in the dtype of x: the tokens' activations in sorted order, each times
+    the weight of its (token, choice) pair."""
+    need_cuda(x, perm, w)
+    need(x.dim() == 2 and x.stride(1) == 1 and perm.dtype == torch.int32 and w.dtype == torch.float32 and w.is_contiguous()
+         and w.numel() == perm.numel(), "moe_scale_gather: x [T, K], an int32 permutation and float32 weights of its length")
+    n, K = perm.numel(), x.shape[1]
+    out = torch.empty((n, K), dtype=x.dtype, device=x.device)
+    f = _f("moe", "rf_moe_scale_gather", c_int, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), x.stride(0), ptr(perm), ptr(w), top, ptr(out), K, n, stream()), "moe_scale_gather")
+    return out
+
+
+def moe_pair_weights(perm: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """w.flat[perm[r]]: the pairs' weights in sorted order, float32 [n]."""
+    need_cuda(perm, w)
+    need(perm.dtype == torch.int32 and w.dtype == torch.float32 and w.is_contiguous() and w.numel() == perm.numel(),
+         "moe_pair_weights: an int32 permutation and float32 weights of its length")
+    n = perm.numel()
+    ws = torch.empty((n,), dtype=torch.float32, device=w.device)
+    f = _f("moe", "rf_moe_pair_weights", c_void_p, c_void_p, c_void_p, c_int, c_void_p)
+    check(f(ptr(perm), ptr(w), ptr(ws), n, stream()), "moe_pair_weights")
+    return ws
 
 
 def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int):
@@ -742,10 +901,15 @@ def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int):
     return perm, inv, tiles, max_tiles
 
 
-def moe_combine(y: torch.Tensor, inv: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_k w[t, k] * y[inv[t*top + k]] in the order of k; y float32 [T*top, H] in sorted order."""
+def moe_combine(y: torch.Tensor, inv: torch.Tensor, w: torch.Tensor | None, top: int | None = None) -> torch.Tensor:
+    """out[t] = sum_k w[t, k] * y[inv[t*top + k]] in the order of k; y float32 [T*top, H] in sorted order.  Without ``w``
+    (``top`` must then be given) the plain sum."""
     need_cuda(y, inv, w)
-    T, top = w.shape
+    if w is None:
+        need(top is not None and top >= 1 and inv.numel() % top == 0, "moe_combine: without weights, top must be given")
+        T = inv.numel() // top
+    else:
+        T, top = w.shape
     need(y.dtype == torch.float32 and y.is_contiguous() and y.shape[0] == T * top, "moe_combine: y must be float32 [T*top, H]")
     H = y.shape[1]
     out = torch.empty((T, H), dtype=torch.float32, device=y.device)

@@ -1,2 +1,3 @@
 from . import qwen2      # registers "Qwen2ForCausalLM"
 from . import rifizen    # registers "Rifizen"
+from . import vilulorn   # registers "Vilulorn"

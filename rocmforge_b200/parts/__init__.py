@@ -14,3 +14,5 @@ from .experts import RoutedExperts
 from .retention import Retention
 from .parallel import ParallelMixer
 from .offsets import PassOffsets
+from .gla import GatedLinearAttention
+from .embedding import LearnedPositions

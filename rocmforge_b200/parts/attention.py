@@ -30,8 +30,15 @@ class GQAAttention(Mixer):
     Options that other designs use, all off by default: ``v_head_dim`` (values of another size than keys),
     ``qk_norm_eps`` (every query and key head divided by its root mean square, x / sqrt(mean(x^2) + eps), no weight,
     before the rotation), ``softcap`` (score <- softcap * tanh(score / softcap) after scaling), ``distance_slopes``
-    (one slope per head: after the cap a score is lowered by slope * (query position - key position)), and ``names``
-    (the tensors' names below the part's prefix, keys q, k, v, o).  Normed heads and values of another size go into the
+    (one slope per head: after the cap a score is lowered by slope * (query position - key position)), ``names``
+    (the tensors' names below the part's prefix, keys q, k, v, o, and g, q_norm, k_norm where they exist),
+    ``qk_norm_weight`` (the normed query heads are multiplied by a weight [head_dim] shared by all of them, the key heads
+    by another), ``chunk`` (position i sees j <= i only inside its own chunk of ``chunk`` positions, chunks counted from
+    position 0 of the sequence, however the prompt is cut into steps), ``gate`` ("sigmoid": the concatenated heads are
+    multiplied by sigmoid(W_g x) before the output projection; W_g reads the same input as q, k, v and is part of the same
+    product), ``shares_kv`` (the mixer has no key and value tensors: the schedule lets it read another execution's
+    cache, ``ScheduleEntry.kv_from``, with queries, mask and everything else of its own) and ``cache_keeps`` (what the
+    cache must keep when other mixers read it with masks of their own: "all", or None for this mixer's own mask).  Normed heads and values of another size go into the
     cache through the per-head writer; a cap and slopes are known to the generic attention and to the tcgen05 prompt
     attention and the clustered decode attention (heads of 64 or 128 with values of the same size), so such a mixer runs
     on the same kernels as one without them.
@@ -42,7 +49,9 @@ class GQAAttention(Mixer):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  o_bias: bool = False, window: Optional[int] = None, position=None,
                  scale: Optional[float] = None, v_head_dim: Optional[int] = None, qk_norm_eps: Optional[float] = None,
-                 softcap: Optional[float] = None, distance_slopes=None, names: Optional[Dict[str, str]] = None):
+                 softcap: Optional[float] = None, distance_slopes=None, names: Optional[Dict[str, str]] = None,
+                 qk_norm_weight: bool = False, chunk: Optional[int] = None, gate: Optional[str] = None,
+                 shares_kv: bool = False, cache_keeps: Optional[str] = None):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
         self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
@@ -56,29 +65,48 @@ class GQAAttention(Mixer):
         if self.distance_slopes is not None and len(self.distance_slopes) != n_heads:
             raise ValueError(f"{len(self.distance_slopes)} distance slopes for {n_heads} heads")
         self.slopes_dev = None
-        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight"}
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                      "g": "g_proj.weight", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
         self.names.update(names or {})
+        self.chunk = int(chunk) if chunk else None
+        if self.chunk is not None and window:
+            raise ValueError("gqa_attention: a window or chunks, not both")
+        if gate not in (None, "sigmoid"):
+            raise ValueError(f"gqa_attention: gate {gate!r} has no kernel (sigmoid)")
+        if cache_keeps not in (None, "all"):
+            raise ValueError(f"gqa_attention: cache_keeps {cache_keeps!r} (all, or None)")
+        self.gate, self.shares_kv, self.cache_keeps = gate, bool(shares_kv), cache_keeps
+        self.qk_norm_weight = bool(qk_norm_weight)
+        if self.qk_norm_weight and qk_norm_eps is None:
+            raise ValueError("gqa_attention: norm weights go with qk_norm_eps")
+        self.q_norm_w = self.k_norm_w = None
         self.q_size = n_heads * head_dim
         self.kv_size = n_kv_heads * head_dim
         self.v_size = n_kv_heads * self.v_head_dim
         self.o_in = n_heads * self.v_head_dim
         # normed heads and values of another size: the per-head cache writer; a cap or slopes: no mma.sync kernel knows them
-        self.plain_projection = self.v_head_dim != head_dim or self.qk_norm_eps is not None
+        self.plain_projection = (self.v_head_dim != head_dim or self.qk_norm_eps is not None or self.gate is not None
+                                 or self.shares_kv)
         self.shaped_scores = self.softcap is not None or self.distance_slopes is not None
         self.plain_only = self.plain_projection or self.shaped_scores
         if self.plain_only and (qkv_bias or o_bias):
-            raise ValueError("gqa_attention: biases do not go with normed heads, a score cap, distance slopes or another value size")
+            raise ValueError("gqa_attention: biases do not go with normed heads, a score cap, distance slopes, another "
+                             "value size, a gate or a borrowed cache")
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         n = self.names
-        s = {
-            n["q"]: ParamSpec((self.q_size, self.hidden)),
-            n["k"]: ParamSpec((self.kv_size, self.hidden)),
-            n["v"]: ParamSpec((self.v_size, self.hidden)),
-            n["o"]: ParamSpec((self.hidden, self.o_in)),
-        }
+        s = {n["q"]: ParamSpec((self.q_size, self.hidden)), n["o"]: ParamSpec((self.hidden, self.o_in))}
+        if not self.shares_kv:
+            s[n["k"]] = ParamSpec((self.kv_size, self.hidden))
+            s[n["v"]] = ParamSpec((self.v_size, self.hidden))
+        if self.gate is not None:
+            s[n["g"]] = ParamSpec((self.o_in, self.hidden))
+        if self.qk_norm_weight:
+            s[n["q_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="ones")
+            if not self.shares_kv:
+                s[n["k_norm"]] = ParamSpec((self.head_dim,), kind="vector", init="ones")
         if self.qkv_bias:
             s["q_proj.bias"] = ParamSpec((self.q_size,), kind="vector")
             s["k_proj.bias"] = ParamSpec((self.kv_size,), kind="vector")
@@ -89,7 +117,13 @@ class GQAAttention(Mixer):
 
     def bind(self, params, compute_dtype):
         n = self.names
-        w = torch.cat([params[n["q"]], params[n["k"]], params[n["v"]]], dim=0)
+        # one product for everything that reads the mixer's input: q | k | v | gate (k, v absent with a borrowed cache)
+        w = torch.cat([params[n["q"]]] + ([] if self.shares_kv else [params[n["k"]], params[n["v"]]])
+                      + ([params[n["g"]]] if self.gate is not None else []), dim=0)
+        self.gate_col = self.q_size + (0 if self.shares_kv else self.kv_size + self.v_size)
+        if self.qk_norm_weight:
+            self.q_norm_w = params[n["q_norm"]]
+            self.k_norm_w = None if self.shares_kv else params[n["k_norm"]].to(self.q_norm_w.dtype)
         b = None
         if self.qkv_bias:
             bs = [params["q_proj.bias"], params["k_proj.bias"], params["v_proj.bias"]]
@@ -111,8 +145,12 @@ class GQAAttention(Mixer):
         return mods
 
     def cache_request(self):
-        return KVRequest(self.n_kv_heads, self.head_dim, self.window,
-                         None if self.v_head_dim == self.head_dim else self.v_head_dim)
+        if self.shares_kv:
+            return None                                   # the schedule names the execution whose cache it reads
+        keeps_all = self.cache_keeps == "all"
+        return KVRequest(self.n_kv_heads, self.head_dim, None if keeps_all else self.window,
+                         None if self.v_head_dim == self.head_dim else self.v_head_dim,
+                         None if keeps_all else self.chunk)
 
     # rows of the query tiles of the two tiled prefill kernels (csrc/attention_prefill.cu, attention_prefill_tc.cu)
     TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
@@ -132,13 +170,20 @@ class GQAAttention(Mixer):
         return np.asarray(tiles, dtype=np.int32).reshape(-1)
 
     def forward(self, ctx, y, cache_view, stream):
-        q = self.project_into_cache(ctx, y, cache_view)                     # rotated q; k, v are in the cache
-        o = self.attend(ctx, q, cache_view)
-        self.o.add_to_stream(ctx, o, stream)
+        self.o.add_to_stream(ctx, self.heads_out(ctx, y, cache_view), stream)
 
     def output(self, ctx, y, cache_view):
-        q = self.project_into_cache(ctx, y, cache_view)
-        return self.o.f32_parts(ctx, self.attend(ctx, q, cache_view))
+        return self.o.f32_parts(ctx, self.heads_out(ctx, y, cache_view))
+
+    def heads_out(self, ctx, y, cache_view):
+        """The concatenated heads (gated, if the mixer has a gate): the output projection's input."""
+        if self.shares_kv and (cache_view is None or cache_view.writes):
+            raise RuntimeError("gqa_attention: a mixer without keys and values must be scheduled with kv_from")
+        q = self.project_into_cache(ctx, y, cache_view)                     # rotated q; k, v are in the cache
+        o = self.attend(ctx, q, cache_view)
+        if self.gate is not None:
+            o = kernels.sigmoid_gate(o, self._gate_cols)
+        return o
 
     def _project_plain(self, ctx, y, view, rot, inv_freq):
         """The projection for heads that are normed or values of another size: one product (K-split partial sums with
@@ -148,10 +193,11 @@ class GQAAttention(Mixer):
         if isinstance(y, ScaledRows):
             y = y.materialize()
         common = dict(compute_dtype=ctx.compute_dtype, rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False),
-                      unit_norm_eps=self.qk_norm_eps)
+                      unit_norm_eps=self.qk_norm_eps, q_norm_weight=self.q_norm_w, k_norm_weight=self.k_norm_w)
+        writes = view.writes and not self.shares_kv
         args = (self.n_heads, self.n_kv_heads, self.head_dim, self.v_head_dim, inv_freq, ctx.tok_seq, ctx.tok_pos,
-                ctx.seq_slot, view.block_table, view.k_pages, view.v_pages, view.writes)
-        if y.shape[0] <= tc.SKINNY_MAX_TOKENS:
+                ctx.seq_slot, view.block_table, view.k_pages, view.v_pages, writes)
+        if self.gate is None and y.shape[0] <= tc.SKINNY_MAX_TOKENS:        # (a gate is read from the product's own output)
             if ctx.uses_tensor_cores(y, w, tc.PARTIAL):
                 splits = tc.split_k_for(w.shape[0], w.shape[1], tokens=y.shape[0])
                 if splits > 1:
@@ -160,7 +206,10 @@ class GQAAttention(Mixer):
                 splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
                 if splits > 1:
                     return kernels.head_norm_kv_write(kernels.gemm_simt(y, w, splits=splits), *args, **common)
-        return kernels.head_norm_kv_write(ctx.matmul(y, w), *args, **common)
+        p = ctx.matmul(y, w)
+        if self.gate is not None:
+            self._gate_cols = p[:, self.gate_col:self.gate_col + self.o_in]
+        return kernels.head_norm_kv_write(p, *args, **common)
 
     def project_into_cache(self, ctx, y, view):
         """q/k/v projection (+ bias), rotation, cache write; returns rotated q [T, >= heads*head_dim].
@@ -203,10 +252,11 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         tiles64, tiles128 = ctx.tables.get("attention_tiles64"), ctx.tables.get("attention_tiles128")
         longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
-        shaped = dict(softcap=self.softcap, slopes=self.slopes_dev)
+        shaped = dict(softcap=self.softcap, slopes=self.slopes_dev, chunk=self.chunk)
+        span = self.window or self.chunk                  # the most keys a query sees
         if self.v_head_dim != hd or (self.shaped_scores and ctx.compute_dtype != torch.bfloat16):
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
-                                             ctx.seq_slot, view.block_table, self.scale, view.window,
+                                             ctx.seq_slot, view.block_table, self.scale, self.window,
                                              v_head_dim=self.v_head_dim, **shaped)
         if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
@@ -215,8 +265,8 @@ class GQAAttention(Mixer):
                 # through distributed shared memory: no scratch memory, no second pass, any context length
                 return kernels.attention_decode_warps(
                     q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
-                    view.block_table, self.scale, view.window,
-                    splits=kernels.decode_splits(ctx.B, nkv, longest, view.window), **shaped)
+                    view.block_table, self.scale, self.window,
+                    splits=kernels.decode_splits(ctx.B, nkv, longest, span), **shaped)
             if not self.shaped_scores and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
                 # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
@@ -230,25 +280,26 @@ class GQAAttention(Mixer):
                 scratch = ctx.model.scratch
                 return kernels.attention_decode(
                     q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
-                    view.block_table, self.scale, view.window, max_chunks,
+                    view.block_table, self.scale, self.window, max_chunks,
                     scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
-                    kernels.tensor_core.register_counters(scratch("attn_decode_counters", n_c, torch.int32)))
+                    kernels.tensor_core.register_counters(scratch("attn_decode_counters", n_c, torch.int32)),
+                    chunk=self.chunk)
         if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and ctx.options.tcgen05_attention and tiles128 is not None and tiles128.numel() > 0
                 and kernels.attention_prefill_tc_supported(nh, nkv, hd)
                 and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
             return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles128,
                                                 ctx.seq_slot, ctx.seq_start, ctx.seq_nnew, ctx.cu_q,
-                                                view.block_table, self.scale, view.window, **shaped)
+                                                view.block_table, self.scale, self.window, **shaped)
         if self.shaped_scores:
             return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
-                                             ctx.seq_slot, view.block_table, self.scale, view.window, **shaped)
+                                             ctx.seq_slot, view.block_table, self.scale, self.window, **shaped)
         if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
                 and tiles64 is not None and tiles64.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
                 and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):
             return kernels.attention_prefill(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles64, ctx.seq_slot,
                                              ctx.seq_start, ctx.seq_nnew, ctx.cu_q, view.block_table, self.scale,
-                                             view.window)
+                                             self.window, chunk=self.chunk)
         return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
-                                         ctx.seq_slot, view.block_table, self.scale, view.window)
+                                         ctx.seq_slot, view.block_table, self.scale, self.window, chunk=self.chunk)
 

@@ -48,10 +48,34 @@ class UnusedTensors(Part):
         return self.specs
 
 
+class ReadsStream(Norm):
+    """Stands where a sub-layer has no norm on its way in: the sub-layer reads the stream itself, rounded to the compute
+    dtype (on the 32-bit path the stream as it is).  It has no tensors.  Whoever updated the stream last may have left
+    the rounded copy in ``stream.prepared``; else one small kernel makes it."""
+
+    def forward(self, ctx, stream, rows=None, deferred_ok=False):
+        from .. import kernels
+        prepared, stream.prepared = stream.prepared, None
+        if rows is not None:
+            raise NotImplementedError("a sub-layer that reads the stream itself reads all of its rows")
+        if prepared is not None and prepared[0] is self and stream.pending is None:
+            return prepared[1]
+        stream.flush()
+        import torch
+        return stream.h if ctx.compute_dtype == torch.float32 else kernels.round_rows(stream.h, ctx.compute_dtype)
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
+
+READS_STREAM = ReadsStream()     # one for all: a block that prepares the next block's input finds it by identity
+
+
 @BLOCKS.register("sandwich")
 class SandwichBlock(Block):
     """x += post1(mixer(norm1(x))); x += post2(ffn(norm2(x))): every sub-layer is normed on its way in and on its way
-    out.  ``ffn`` (with norm2 and post2) may be None: the block is then its first half.
+    out.  ``ffn`` (with norm2 and post2) may be None: the block is then its first half.  ``norm1`` / ``norm2`` None: that
+    sub-layer has a norm on its way out only and reads the stream itself, x += post(sub-layer(x)).
 
     The outputs of the sub-layers, their norms and the sums are 32-bit.  One kernel per sub-layer forms the mixer's
     merge (if it hands out a ``NormedMean``), the out-norm, the sum into the stream, a row vector that the schedule
@@ -61,27 +85,33 @@ class SandwichBlock(Block):
 
     def __init__(self, norm1: Norm, mixer: Mixer, post1: Norm, norm2: Norm = None, ffn: FeedForward = None,
                  post2: Norm = None, names: Dict[str, str] = None):
-        if (ffn is None) != (norm2 is None) or (ffn is None) != (post2 is None):
-            raise ValueError("sandwich block: norm2, ffn and post2 come together or not at all")
-        self.norm1, self.mixer, self.post1 = norm1, mixer, post1
-        self.norm2, self.ffn, self.post2 = norm2, ffn, post2
+        if (ffn is None) != (post2 is None) or (ffn is None and norm2 is not None):
+            raise ValueError("sandwich block: ffn and post2 come together or not at all, norm2 only with them")
+        self.norm1, self.mixer, self.post1 = norm1 if norm1 is not None else READS_STREAM, mixer, post1
+        self.norm2 = (norm2 if norm2 is not None else READS_STREAM) if ffn is not None else None
+        self.ffn, self.post2 = ffn, post2
         self.names = dict(names)
 
     def sub_parts(self) -> Dict[str, Part]:
-        out = {self.names["norm1"]: self.norm1, self.names["post1"]: self.post1}
+        out = {self.names["post1"]: self.post1}
+        if self.norm1 is not READS_STREAM:
+            out[self.names["norm1"]] = self.norm1
         if hasattr(self.mixer, "leaf_parts"):                # a mixer made of mixers: its halves have prefixes of their own
             for sub, part in self.mixer.leaf_parts().items():
                 out[self.names["mixer"] + sub] = part
         else:
             out[self.names["mixer"]] = self.mixer
         if self.ffn is not None:
-            out.update({self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn, self.names["post2"]: self.post2})
-        elif self.names.get("norm2") is not None and self.names.get("post2") is not None:
-            # a layer without feed-forward: a folder that stores the second pair of norms all the same is not at fault
+            out.update({self.names["ffn"]: self.ffn, self.names["post2"]: self.post2})
+            if self.norm2 is not READS_STREAM:
+                out[self.names["norm2"]] = self.norm2
+        else:
+            # a layer without feed-forward: a folder that stores the second sub-layer's norms all the same is not at fault
             from ..weights.spec import ParamSpec
-            size = self.norm1.size
-            out[""] = UnusedTensors({self.names[n] + self.norm1.param_name: ParamSpec((size,), kind="vector", init="ones", optional=True)
-                                     for n in ("norm2", "post2")})
+            unused = [n for n in ("norm2", "post2") if self.names.get(n) is not None]
+            if unused:
+                out[""] = UnusedTensors({self.names[n] + self.post1.param_name:
+                                         ParamSpec((self.post1.size,), kind="vector", init="ones", optional=True) for n in unused})
         return out
 
     def entry_norm(self):
@@ -105,8 +135,10 @@ class SandwichBlock(Block):
             nxt = None
         stream.flush()
         stream.prepared = None
+        import torch
         y = kernels.branch_norm_add(stream.h, branches, weight, eps, ctx.compute_dtype, extra=extra,
-                                    next_weight=nxt[0] if nxt is not None else None)
+                                    next_weight=nxt[0] if nxt is not None else None,
+                                    next_rounded=next_norm is READS_STREAM and ctx.compute_dtype != torch.float32)
         if y is not None:
             stream.prepared = (next_norm, y)
 

@@ -30,6 +30,31 @@ class TokenEmbedding(Part):
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
         return kernels.embed(self.weight, token_ids)
 
+    def forward_with(self, ctx, token_ids: torch.Tensor, positions: "LearnedPositions" = None, rounded: bool = False):
+        """(x, y): x = E[token] (+ positions' vector of the token's position), and y = x in the compute dtype if
+        ``rounded`` (for a first layer that reads the stream itself), else None; one kernel."""
+        return kernels.embed_positions(self.weight, token_ids, positions.table if positions is not None else None,
+                                       ctx.tok_pos if positions is not None else None,
+                                       rounded=rounded and ctx.compute_dtype != torch.float32)
+
+
+class LearnedPositions(Part):
+    """A learned vector per position, [positions, hidden], added to the embedding (not scaled).  Sequences cannot grow
+    beyond the table (the model's longest sequence is set from it)."""
+
+    def __init__(self, positions: int, hidden: int, param_name: str = "weight"):
+        self.positions, self.hidden, self.param_name = positions, hidden, param_name
+        self.table: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.param_name: ParamSpec((self.positions, self.hidden))}
+
+    def bind(self, params, compute_dtype):
+        self.table = params[self.param_name]
+
+    def cuda_modules(self, compute_dtype):
+        return ["elementwise"]
+
 
 class OutputHead(Part):
     """logits = W y in float32; with tied embeddings W is the embedding matrix itself

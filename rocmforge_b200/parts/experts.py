@@ -22,12 +22,29 @@ class RoutedExperts(FeedForward):
     choices, in 32-bit: a token's result does not depend on the rest of the batch.
     Tensors: ``router`` [E, H], ``router.b`` [E], ``e<i>.gate`` / ``.up`` [F, H], ``e<i>.down`` [H, F]
     (``names`` may rename router, router_bias, gate, up, down; ``expert_prefix`` the "e").
+
+    What other designs change, as parameters: ``scoring`` "sigmoid" weights a chosen expert by the sigmoid of its own
+    logit, not renormalised (the choice is still by the largest logits); ``weight_on`` "input" multiplies the expert's
+    input by the weight instead of its output, out = sum_e expert_e(w_e y) (an expert is not linear, so the two differ;
+    the products being linear, w (W y) is formed in the first product's epilogue, in 32-bit, before the activation);
+    ``activation`` "clamped_glu" is g sigmoid(glu_alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
     """
 
     def __init__(self, hidden: int, intermediate: int, n_experts: int, top: int, *, router_bias: bool = True,
-                 names: Optional[Dict[str, str]] = None, expert_prefix: str = "e"):
+                 names: Optional[Dict[str, str]] = None, expert_prefix: str = "e", scoring: str = "softmax_of_chosen",
+                 weight_on: str = "output", activation: str = "silu", limit: Optional[float] = None, glu_alpha: float = 1.702):
         if not 1 <= top <= n_experts:
             raise ValueError(f"routed experts: top {top} of {n_experts} experts")
+        if scoring not in kernels.MOE_SCORINGS:
+            raise ValueError(f"routed experts: scoring {scoring!r} (known: {sorted(kernels.MOE_SCORINGS)})")
+        if weight_on not in ("output", "input") or activation not in ("silu", "clamped_glu"):
+            raise ValueError(f"routed experts: weight_on {weight_on!r} / activation {activation!r} have no kernel")
+        if weight_on == "input" and activation == "silu":
+            raise ValueError("routed experts: weights on the inputs are built for the clamped activation only")
+        if activation == "clamped_glu" and not (limit is not None and limit > 0):
+            raise ValueError("routed experts: the clamped activation needs a positive limit")
+        self.scoring, self.weight_on, self.activation = scoring, weight_on, activation
+        self.limit, self.glu_alpha = (float(limit) if limit is not None else None), float(glu_alpha)
         self.hidden, self.intermediate, self.n_experts, self.top = hidden, intermediate, n_experts, top
         self.router_bias = router_bias
         self.names = {"router": "router", "router_bias": "router.b", "gate": "gate", "up": "up", "down": "down"}
@@ -66,9 +83,11 @@ class RoutedExperts(FeedForward):
             y = y.materialize()
         T = y.shape[0]
         z = ctx.matmul(y, self.router_w, self.router_b, out_f32=True)         # 32-bit sums of exact products
-        idx, w = kernels.moe_route(z, self.top)
+        idx, w = kernels.moe_route(z, self.top, self.scoring)
         n = T * self.top
         tc = kernels.tensor_core
+        if self.weight_on == "input" or self.activation != "silu":
+            return self._output_general(ctx, y, idx, w, n)
         if (ctx.compute_dtype == torch.bfloat16 and ctx.options.tensor_core_gemm
                 and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.SWIGLU)
                 and tc.grouped_supported(self.hidden, self.intermediate, tc.F32)):
@@ -84,6 +103,32 @@ class RoutedExperts(FeedForward):
         a = kernels.swiglu(gu)                                                               # [n, F], sorted rows
         d = kernels.gemm_simt_grouped(a, self.down, tiles, max_tiles, rows, n, out_f32=True)
         return kernels.moe_combine(d, inv, w)
+
+    def _output_general(self, ctx, y, idx, w, n):
+        """Weights on the experts' inputs and/or another activation: the first grouped product leaves gate and up as they
+        are, one kernel scales each sorted row by its pair's weight (in 32-bit, before anything is clamped) and applies
+        the activation, and with the weights spent on the inputs the choices of a token are summed plainly."""
+        tc = kernels.tensor_core
+        on_input = self.weight_on == "input"
+        use_tc = (ctx.compute_dtype == torch.bfloat16 and ctx.options.tensor_core_gemm
+                  and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.STORE)
+                  and tc.grouped_supported(self.hidden, self.intermediate, tc.F32))
+        rows = kernels.MOE_TILE_TC if use_tc else (kernels.MOE_TILE_SMALL if n <= 16 * self.n_experts else kernels.MOE_TILE_LARGE)
+        perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
+        ws = kernels.moe_pair_weights(perm, w) if on_input else None
+        if use_tc:
+            gu = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.STORE)
+        else:
+            gu = kernels.gemm_simt_grouped(y, self.gate_up, tiles, max_tiles, rows, n, row_map=perm, row_div=self.top)
+        if self.activation == "clamped_glu":
+            a = kernels.clamped_glu(gu, self.limit, self.glu_alpha, row_scale=ws)
+        else:
+            a = kernels.swiglu(gu)
+        if use_tc:
+            d = tc.gemm_tc_grouped(a, self.down, tiles, max_tiles, mode=tc.F32)
+        else:
+            d = kernels.gemm_simt_grouped(a, self.down, tiles, max_tiles, rows, n, out_f32=True)
+        return kernels.moe_combine(d, inv, None if on_input else w, top=self.top)
 
     def forward(self, ctx, y, stream):
         stream.add_pending(self.output(ctx, y))

@@ -1,6 +1,8 @@
 """Rotary position encoding, NeoX pairing over the whole head."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import POSITIONS, PositionEncoding
@@ -18,9 +20,13 @@ class NeoxRope(PositionEncoding):
     once in double precision, rounded to float32 and shared by every kernel, so that
     all of them (and the plain implementation) rotate by the same angle
     float32(pos) * float32(freq).
+
+    ``scaling`` (a dict factor, low, high, original) stretches the frequencies by wavelength l = 2 pi / f, as the
+    Llama 3.1 models do: f stays where l < original/high, becomes f / factor where l > original/low, and in between
+    (1 - s) f / factor + s f with s = (original/l - low) / (high - low).
     """
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False, scaling=None):
         rot = head_dim if rotary_dim is None else int(rotary_dim)
         if head_dim % 2 or rot % 2 or not 0 < rot <= head_dim:
             raise ValueError(f"rotary encoding needs an even head_dim and an even rotary_dim in (0, head_dim]; "
@@ -28,9 +34,21 @@ class NeoxRope(PositionEncoding):
         self.head_dim, self.rotary_dim, self.interleaved = head_dim, rot, bool(interleaved)
         self.theta = float(theta)
         i = torch.arange(rot // 2, dtype=torch.float64)
-        self.inv_freq_host = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64),
-                                              2.0 * i / rot)).to(torch.float32)
+        freq = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / rot)
+        self.scaling = None if scaling is None else {k: float(scaling[k]) for k in ("factor", "low", "high", "original")}
+        if self.scaling is not None:
+            freq = self.scaled_by_wavelength(freq, **self.scaling)
+        self.inv_freq_host = freq.to(torch.float32)
         self.inv_freq = None
+
+    @staticmethod
+    def scaled_by_wavelength(freq: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+        if not (factor > 0 and high > low and original > 0):
+            raise ValueError(f"frequency scaling needs factor > 0, high > low and original > 0; got {factor}, {low}, {high}, {original}")
+        wave = 2.0 * math.pi / freq
+        blend = (original / wave - low) / (high - low)
+        mixed = (1.0 - blend) * freq / factor + blend * freq
+        return torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
 
     def prepare(self, device):
         self.inv_freq = self.inv_freq_host.to(device)

@@ -172,3 +172,71 @@ def write_rifizen(cfg: dict, folder: str, dtype: str = "float32") -> None:
     c = arch.config_cls.from_dict(config_dict(cfg))
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     rf.write_model_folder(folder, c.to_dict(), arch.build(c).param_specs(), cfg["seed"], dt)
+
+
+# --------------------------------------------------------------------------- Vilulorn
+
+def _gla(*, heads, dim, vdim, tau, mlp):
+    return {"type": "gla", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}, "mlp": mlp}
+
+
+def _chunk_attention(*, heads, kv_heads, dim, vdim, chunk, scale, rot_dims, rot_base, scaling=None, kv_from=None, mlp):
+    rot = {"dims": rot_dims, "base": rot_base}
+    if scaling is not None:
+        rot["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk}, "scale": scale, "rot": rot}
+    if kv_from is not None:
+        mixer["kv_from"] = kv_from
+    return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+
+def _scored(ff, experts, top, limit):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+
+# Sizes that differ from each other in every respect: the order of the two kinds of layer, values of another size than
+# keys, value columns that do not fill a warp's share, key sizes that are no multiple of 32, decay ranks that are no
+# multiple of 8, tau of 1 and large, chunks below a page, of a page, and above one, a wholly rotated and a partly rotated
+# head with and without stretched frequencies, one kv head for all and as many as heads, layers that borrow keys with
+# the lender's chunk size and with another, a layer without feed-forward, one expert a token and several, limits that
+# bite.  ``ranks``: rows of each gla layer's first decay matrix (a tensor's shape, not a key of config.json).
+VILULORN_A = dict(seed=21, architecture="Vilulorn", vocab=96, width=64, max_positions=400, norm={"eps": 1e-5}, ranks={1: 5, 3: 8},
+                  layers=[_chunk_attention(heads=4, kv_heads=2, dim=16, vdim=24, chunk=7, scale=0.4, rot_dims=8, rot_base=100.0,
+                                           mlp=_scored(20, 5, 2, 0.5)),
+                          _gla(heads=2, dim=24, vdim=12, tau=1.0, mlp=None),
+                          _chunk_attention(heads=4, kv_heads=2, dim=16, vdim=24, chunk=64, scale=0.25, rot_dims=8, rot_base=100.0,
+                                           kv_from=0, mlp=_scored(24, 3, 3, 4.0)),
+                          _gla(heads=1, dim=40, vdim=20, tau=4.0, mlp=_scored(16, 4, 1, 1.0))])
+VILULORN_B = dict(seed=22, architecture="Vilulorn", vocab=200, width=128, max_positions=512, norm={"eps": 1e-6}, ranks={0: 16, 3: 3},
+                  layers=[_gla(heads=3, dim=64, vdim=32, tau=16.0, mlp=_scored(48, 8, 1, 2.0)),
+                          _chunk_attention(heads=3, kv_heads=3, dim=40, vdim=40, chunk=100, scale=0.16, rot_dims=40, rot_base=1e4,
+                                           scaling=(8.0, 1.0, 4.0, 64), mlp=None),
+                          _chunk_attention(heads=3, kv_heads=3, dim=40, vdim=40, chunk=100, scale=0.3, rot_dims=40, rot_base=1e4,
+                                           scaling=(8.0, 1.0, 4.0, 64), kv_from=1, mlp=_scored(40, 6, 2, 1.5)),
+                          _gla(heads=2, dim=96, vdim=72, tau=7.0, mlp=_scored(32, 2, 2, 3.0))])
+VILULORN_C = dict(seed=23, architecture="Vilulorn", vocab=300, width=256, max_positions=1024, norm={"eps": 1e-6}, ranks={0: 32, 2: 16},
+                  layers=[_gla(heads=2, dim=128, vdim=128, tau=10.0, mlp=_scored(96, 6, 3, 2.5)),
+                          _chunk_attention(heads=8, kv_heads=2, dim=64, vdim=64, chunk=130, scale=0.125, rot_dims=32, rot_base=1e6,
+                                           scaling=(4.0, 1.0, 4.0, 256), mlp=_scored(64, 4, 2, 2.0)),
+                          _gla(heads=4, dim=32, vdim=64, tau=2.0, mlp=_scored(64, 16, 1, 6.0)),
+                          _chunk_attention(heads=4, kv_heads=1, dim=128, vdim=128, chunk=33, scale=0.09, rot_dims=64, rot_base=1e4,
+                                           mlp=_scored(128, 3, 1, 1.0)),
+                          _chunk_attention(heads=8, kv_heads=2, dim=64, vdim=64, chunk=130, scale=0.2, rot_dims=32, rot_base=1e6,
+                                           scaling=(4.0, 1.0, 4.0, 256), kv_from=1, mlp=_scored(64, 4, 4, 2.0))])
+VILULORN_CONFIGS = {"VA": VILULORN_A, "VB": VILULORN_B, "VC": VILULORN_C}
+
+
+def vilulorn_config(cfg: dict):
+    """(typed configuration, the dict that goes into config.json)."""
+    from rocmforge_b200.config import architecture_for
+    raw = {k: v for k, v in cfg.items() if k not in ("seed", "ranks")}
+    shapes = {f"l{i}.mix.a1": (r, cfg["width"]) for i, r in cfg.get("ranks", {}).items()}
+    return architecture_for("Vilulorn").config_cls.from_dict(raw, shapes=shapes), raw
+
+
+def write_vilulorn(cfg: dict, folder: str, dtype: str = "float32") -> None:
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import architecture_for
+    c, raw = vilulorn_config(cfg)
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    rf.write_model_folder(folder, raw, architecture_for("Vilulorn").build(c).param_specs(), cfg["seed"], dt)
