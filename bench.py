@@ -434,18 +434,37 @@ def kernel_table(fn, top=14):
     return rows[:top]
 
 
-def rifizen_points(pk, seed, widths=(1024, 2048), tokens=PREFILL_TOKENS, batches=(8, 64), steps=64, warmup=8):
-    """Prefill and decode of the Rifizen design at layer sizes of a real model, beside the dense decoder at equal
-    size, with the heaviest kernels of each step."""
+def vilulorn_shape(width, layers=4):
+    """A Vilulorn configuration with layers of the size a real model has: gated linear attention with a state of
+    128 x 128 per head alternating with attention in chunks of 1,024 (128-element heads, half of each rotated, a quarter
+    as many kv heads; the second attention layer reads the first one's keys), 16 experts of width each (2 per token) in
+    every layer.  And the Rifizen configuration of equal width, heads and depth (its closest relative here: a matrix state
+    per head, attention over a bounded span, routed experts)."""
+    heads = width // 128
+    gla = dict(heads=heads, dim=128, vdim=128, tau=16.0)
+    att = dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, mask={"size": 1024}, scale=128 ** -0.5,
+               rot=dict(dims=64, base=1e6, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    moe = dict(kind="moe", expert=dict(ff=width, limit=7.0), router=dict(experts=16, top=2))
+    mixers = [("gla", gla), ("attention", att), ("gla", gla), ("attention", dict(att, kv_from=1))]
+    vil = dict(architecture="Vilulorn", vocab=32000, width=width, max_positions=8192, norm=dict(eps=1e-6),
+               layers=[dict(type=mixers[i % 4][0], mixer=mixers[i % 4][1], mlp=moe) for i in range(layers)])
+    return vil, rifizen_shape(width, layers)[0]
+
+
+def rifizen_points(pk, seed, widths=(1024, 2048), tokens=PREFILL_TOKENS, batches=(8, 64), steps=64, warmup=8,
+                   names=("rifizen", "dense"), archs=("Rifizen", "Qwen2ForCausalLM"), shapes=None):
+    """Prefill and decode of one design at layer sizes of a real model, beside another at equal size (by default Rifizen
+    beside the dense decoder), with the heaviest kernels of each step."""
     import torch
     import rocmforge_b200 as rf
     from rocmforge_b200 import StepRequest
     from rocmforge_b200.config import architecture_for
+    shapes = shapes or rifizen_shape
     out = {}
     for width in widths:
         point = {}
-        for name, raw in zip(("rifizen", "dense"), rifizen_shape(width)):
-            arch = architecture_for("Rifizen" if name == "rifizen" else "Qwen2ForCausalLM")
+        for name, arch_name, raw in zip(names, archs, shapes(width)):
+            arch = architecture_for(arch_name)
             cfg = arch.config_cls.from_dict(raw)
             model = rf.Model.random(cfg, seed=seed, dtype=torch.bfloat16)
             V = model.spec.vocab_size
@@ -545,7 +564,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b", "rifizen", "vilulorn"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
                     help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
@@ -573,6 +592,12 @@ def main():
         print(json.dumps({"only": "rifizen", "tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
                           "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
                           **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup)}))
+        return 0
+    if args.only == "vilulorn":
+        print(json.dumps({"only": "vilulorn", "tokens": PREFILL_TOKENS, "prompt_len": PROMPT_LEN,
+                          "peaks": {k: pk[k] for k in ("hbm_gbs", "bf16_tflops") if k in pk},
+                          **rifizen_points(pk, args.seed, steps=min(args.steps, 64), warmup=warmup, names=("vilulorn", "rifizen"),
+                                           archs=("Vilulorn", "Rifizen"), shapes=vilulorn_shape)}))
         return 0
     if args.only in ("0.5b", "14b"):
         print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))

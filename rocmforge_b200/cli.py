@@ -22,7 +22,7 @@ import time
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="rocmforge", description="B200-native generation for Qwen2.5 models")
+    ap = argparse.ArgumentParser(prog="rocmforge", description="B200-native generation for the registered model designs")
     ap.add_argument("-m", "--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("-p", "--prompt", action="append", default=[], help="input prompt (repeat for a batch)")
     ap.add_argument("--prompt-ids", action="append", default=[], help="prompt as comma-separated token ids")

@@ -177,6 +177,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tcgen05_wait_ld();
                 if (!SWAP) {
                     // lane = token m, registers = 32 consecutive weight rows n
+                    if constexpr (GROUPED) {
+                        const TcGroup& grp = *reinterpret_cast<const TcGroup*>(&grp_arg);
+                        if (p.mode == EPI_CLAMPGLU) {
+                            epilogue_clamped_glu<CH>(p, r, row_a, tile_b * BN + c0, grp.row_scale, grp.limit, grp.alpha);
+                            continue;
+                        }
+                    }
                     epilogue_rows<CH>(p, r, row_a, tile_b * BN + c0);
                 } else {
                     // lane = weight row n, registers = consecutive tokens m
@@ -359,7 +366,7 @@ extern "C" {
 int rf_gemm_tc_supported(int M, int N, int K, int mode) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8) return 0;                              // TMA needs 16-byte row strides
-    if (mode == EPI_SWIGLU && (N % 2)) return 0;
+    if ((mode == EPI_SWIGLU || mode == EPI_CLAMPGLU) && (N % 2)) return 0;
     return encode_fn() != nullptr;
 }
 
@@ -383,22 +390,37 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
 // Many weight matrices in one launch (see GROUPED above): X [n_rows, K] holds the rows sorted by group, W [groups, N, K]
 // the stacked weights, tiles the table of row tiles of at most 128 rows (max_tiles of them at most); out [n_rows, N]
 // (mode STORE / F32) or [n_rows, N/2] (SWIGLU on row-interleaved gate/up weights).
-int rf_gemm_tc_grouped(const void* X, int ldx, int n_rows, const void* W, int groups, int N, int K, void* out, int ldo,
-                       int mode, const int* tiles, int max_tiles, int* status, cudaStream_t st) {
+static int gemm_tc_grouped(const void* X, int ldx, int n_rows, const void* W, int groups, int N, int K, void* out, int ldo,
+                           int mode, const int* tiles, int max_tiles, int* status, cudaStream_t st, const float* row_scale,
+                           float limit, float alpha) {
     if (n_rows <= 0 || max_tiles <= 0) return 0;
-    if (!rf_gemm_tc_supported(n_rows, N, K, mode) || (mode != EPI_STORE && mode != EPI_F32 && mode != EPI_SWIGLU))
+    if (!rf_gemm_tc_supported(n_rows, N, K, mode) ||
+        (mode != EPI_STORE && mode != EPI_F32 && mode != EPI_SWIGLU && mode != EPI_CLAMPGLU))
         return RF_ERR_UNSUPPORTED;
     if (max_tiles > 65535) return RF_ERR_UNSUPPORTED;
     CUtensorMap ma, mb;
     int e;
     TcParams p{out, nullptr, 0, n_rows, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
-    const TcGroup grp{tiles, N};
+    const TcGroup grp{tiles, N, row_scale, limit, alpha};
     if (N > 128) {
         if ((e = make_map(&ma, X, n_rows, K, ldx, TC_BM)) || (e = make_map(&mb, W, (long long)groups * N, K, K, 256))) return e;
         return launch_cfg<256, false, 4, false, true>(ma, mb, p, dim3((N + 255) / 256, max_tiles, 1), st, nullptr, 1, &grp);
     }
     if ((e = make_map(&ma, X, n_rows, K, ldx, TC_BM)) || (e = make_map(&mb, W, (long long)groups * N, K, K, 128))) return e;
     return launch_cfg<128, false, 6, false, true>(ma, mb, p, dim3((N + 127) / 128, max_tiles, 1), st, nullptr, 1, &grp);
+}
+int rf_gemm_tc_grouped(const void* X, int ldx, int n_rows, const void* W, int groups, int N, int K, void* out, int ldo,
+                       int mode, const int* tiles, int max_tiles, int* status, cudaStream_t st) {
+    if (mode == EPI_CLAMPGLU) return RF_ERR_BAD_ARG;              // that mode comes with its constants, below
+    return gemm_tc_grouped(X, ldx, n_rows, W, groups, N, K, out, ldo, mode, tiles, max_tiles, status, st, nullptr, 0.f, 0.f);
+}
+// Mode CLAMPGLU: out [n_rows, N/2] = g sigmoid(alpha g) (u + 1) of the row-interleaved gate/up product, each row first
+// times row_scale[row] (float [n_rows] in sorted order; null: 1), g = min(gate, limit), u = clamp(up, -limit, limit).
+int rf_gemm_tc_grouped_glu(const void* X, int ldx, int n_rows, const void* W, int groups, int N, int K, void* out, int ldo,
+                           const int* tiles, int max_tiles, const float* row_scale, float limit, float alpha, int* status,
+                           cudaStream_t st) {
+    return gemm_tc_grouped(X, ldx, n_rows, W, groups, N, K, out, ldo, EPI_CLAMPGLU, tiles, max_tiles, status, st, row_scale,
+                           limit, alpha);
 }
 
 // Weights as rows, for M <= 256 tokens in tiles of up to 128 (the tiles of one weight tile are neighbours in the grid,

@@ -10,7 +10,7 @@
 #define TC_THREADS 192
 #define TC_WAIT_LIMIT_NS 2000000000ULL      // 2 s
 
-enum { EPI_STORE = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_PARTIAL = 4, EPI_RESNORM = 5 };
+enum { EPI_STORE = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_PARTIAL = 4, EPI_RESNORM = 5, EPI_CLAMPGLU = 6 };
 
 // What the weights-as-rows kernel needs to finish a residual update and prepare the norm that follows it
 // (mode EPI_RESNORM), and to apply a norm that was prepared that way to its own input (ss_in).
@@ -52,6 +52,10 @@ struct TcNoNorm {};
 struct TcGroup {
     const int* tiles;
     int group_n;
+    // EPI_CLAMPGLU (row-interleaved gate/up weights, like EPI_SWIGLU): every output row is first multiplied by
+    // row_scale[row] (null: 1), then a = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit)
+    const float* row_scale;
+    float limit, alpha;
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -266,6 +270,37 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& p, const uint32_t*
 #pragma unroll
     for (int j = 0; j < CH; ++j)
         if (n0 + j < p.N) dst[j] = (p.mode == EPI_RESIDUAL ? dst[j] : 0.f) + v[j];
+}
+
+// The gated unit with clamped halves on row-interleaved gate/up columns (EPI_CLAMPGLU): lane = row m, registers = CH
+// consecutive columns.  The row's scale is applied to the 32-bit sums before anything is clamped.
+__device__ __forceinline__ float clamped_glu_fast(float g, float u, float sc, float limit, float alpha) {
+    g = fminf(g * sc, limit);
+    u = fminf(fmaxf(u * sc, -limit), limit);
+    return __fdividef(g, 1.f + __expf(-alpha * g)) * (u + 1.f);
+}
+template <int CH>
+__device__ __forceinline__ void epilogue_clamped_glu(const TcParams& p, const uint32_t* r, int m, int n0,
+                                                     const float* row_scale, float limit, float alpha) {
+    if (m >= p.M) return;
+    const float sc = row_scale != nullptr ? row_scale[m] : 1.f;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + (n0 >> 1);
+    if (n0 + CH <= p.N && !(reinterpret_cast<uintptr_t>(o) & 15)) {
+#pragma unroll
+        for (int j = 0; j < CH; j += 16) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                w[q] = pack_bf16x2(clamped_glu_fast(__uint_as_float(r[j + 4 * q]), __uint_as_float(r[j + 4 * q + 1]), sc, limit, alpha),
+                                   clamped_glu_fast(__uint_as_float(r[j + 4 * q + 2]), __uint_as_float(r[j + 4 * q + 3]), sc, limit, alpha));
+            *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < CH; j += 2)
+        if (n0 + j + 1 < p.N)
+            o[j >> 1] = __float2bfloat16_rn(clamped_glu_fast(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), sc, limit, alpha));
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).

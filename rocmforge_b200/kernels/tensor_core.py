@@ -8,7 +8,7 @@ import torch
 
 from ._ffi import KernelError, sm_count as device_sm_count, c_float, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
 
-STORE, F32, RESIDUAL, SWIGLU, PARTIAL, RESNORM = 0, 1, 2, 3, 4, 5
+STORE, F32, RESIDUAL, SWIGLU, PARTIAL, RESNORM, CLAMPGLU = 0, 1, 2, 3, 4, 5, 6
 SKINNY_MAX_TOKENS = 128     # above it the large-M kernels stream the weights better (7B shape, decode step: 128 tokens
                             # 5.09 ms skinny / 6.38 ms clustered; 192 tokens as tiles of 64: 7.78 / 6.73)
 
@@ -167,14 +167,17 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
 
 def grouped_supported(N: int, K: int, mode: int) -> bool:
     """Whether the grouped tensor-core product takes weights [groups, N, K] in this mode."""
-    return mode in (STORE, F32, SWIGLU) and supported(128, N, K, mode)
+    return mode in (STORE, F32, SWIGLU, CLAMPGLU) and supported(128, N, K, mode)
 
 
-def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, *, mode: int = STORE) -> torch.Tensor:
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_tiles: int, *, mode: int = STORE,
+                    row_scale: Optional[torch.Tensor] = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
     """One launch for many weight matrices: ``x`` [n, K] holds rows sorted by group, ``w`` [groups, N, K] the stacked
     weights, ``tiles`` the table that ``kernels.moe_sort`` built for row tiles of 128.  STORE -> bf16 [n, N];
-    F32 -> f32 [n, N]; SWIGLU -> bf16 [n, N/2] from row-interleaved gate/up weights."""
-    need_cuda(x, w, tiles)
+    F32 -> f32 [n, N]; SWIGLU -> bf16 [n, N/2] from row-interleaved gate/up weights; CLAMPGLU -> bf16 [n, N/2] =
+    g sigmoid(alpha g) (u + 1) with g = min(s gate, limit), u = clamp(s up, -limit, limit), s = row_scale[row] (float32 [n]
+    in sorted order; 1 without), applied to the 32-bit sums."""
+    need_cuda(x, w, tiles, row_scale)
     need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 3 and x.stride(1) == 1
          and w.is_contiguous() and x.shape[1] == w.shape[2], "grouped gemm: x [n, K] and w [groups, N, K] in bfloat16")
     need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0,
@@ -183,8 +186,17 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, tiles: torch.Tensor, max_t
     n, K = x.shape
     G, N, _ = w.shape
     need(grouped_supported(N, K, mode), f"grouped gemm: {N}x{K} in mode {mode} is not supported")
-    cols = N // 2 if mode == SWIGLU else N
+    cols = N // 2 if mode in (SWIGLU, CLAMPGLU) else N
     out = torch.empty((n, cols), dtype=torch.float32 if mode == F32 else torch.bfloat16, device=x.device)
+    if mode == CLAMPGLU:
+        need(limit > 0 and (row_scale is None or (row_scale.dtype == torch.float32 and row_scale.is_contiguous()
+                                                  and row_scale.numel() >= n)),
+             "grouped gemm: the clamped unit needs a positive limit and float32 row scales [n]")
+        f = _f("rf_gemm_tc_grouped_glu", c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+               c_int, c_void_p, c_float, c_float, c_void_p, c_void_p)
+        check(f(ptr(x), x.stride(0), n, ptr(w), G, N, K, ptr(out), out.stride(0), ptr(tiles), max_tiles, ptr(row_scale),
+                float(limit), float(alpha), ptr(status_word(x.device)), stream()), f"gemm_tc_grouped ({G} x {N}x{K}, clamped unit)")
+        return out
     f = _f("rf_gemm_tc_grouped", c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
            c_int, c_void_p, c_void_p)
     check(f(ptr(x), x.stride(0), n, ptr(w), G, N, K, ptr(out), out.stride(0), mode, ptr(tiles), max_tiles,

@@ -105,25 +105,29 @@ class RoutedExperts(FeedForward):
         return kernels.moe_combine(d, inv, w)
 
     def _output_general(self, ctx, y, idx, w, n):
-        """Weights on the experts' inputs and/or another activation: the first grouped product leaves gate and up as they
-        are, one kernel scales each sorted row by its pair's weight (in 32-bit, before anything is clamped) and applies
-        the activation, and with the weights spent on the inputs the choices of a token are summed plainly."""
+        """Weights on the experts' inputs and/or another activation: each sorted row of the first grouped product is
+        scaled by its pair's weight (in 32-bit, before anything is clamped) and the activation applied, in that product's
+        epilogue on the tensor-core path and by a kernel of its own otherwise; with the weights spent on the inputs the
+        choices of a token are summed plainly."""
         tc = kernels.tensor_core
         on_input = self.weight_on == "input"
         use_tc = (ctx.compute_dtype == torch.bfloat16 and ctx.options.tensor_core_gemm
-                  and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.STORE)
+                  and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.CLAMPGLU)
                   and tc.grouped_supported(self.hidden, self.intermediate, tc.F32))
         rows = kernels.MOE_TILE_TC if use_tc else (kernels.MOE_TILE_SMALL if n <= 16 * self.n_experts else kernels.MOE_TILE_LARGE)
         perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
         ws = kernels.moe_pair_weights(perm, w) if on_input else None
-        if use_tc:
-            gu = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.STORE)
+        if use_tc and self.activation == "clamped_glu":
+            # the scale and the activation happen in the first product's epilogue, on its 32-bit sums
+            a = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.CLAMPGLU,
+                                   row_scale=ws, limit=self.limit, alpha=self.glu_alpha)
         else:
-            gu = kernels.gemm_simt_grouped(y, self.gate_up, tiles, max_tiles, rows, n, row_map=perm, row_div=self.top)
-        if self.activation == "clamped_glu":
-            a = kernels.clamped_glu(gu, self.limit, self.glu_alpha, row_scale=ws)
-        else:
-            a = kernels.swiglu(gu)
+            if use_tc:
+                gu = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.STORE)
+            else:
+                gu = kernels.gemm_simt_grouped(y, self.gate_up, tiles, max_tiles, rows, n, row_map=perm, row_div=self.top)
+            a = (kernels.clamped_glu(gu, self.limit, self.glu_alpha, row_scale=ws) if self.activation == "clamped_glu"
+                 else kernels.swiglu(gu))
         if use_tc:
             d = tc.gemm_tc_grouped(a, self.down, tiles, max_tiles, mode=tc.F32)
         else:

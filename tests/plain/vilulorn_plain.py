@@ -134,14 +134,25 @@ def clamped_expert(x, W, pre, limit: float):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ W[pre + "down"].T
 
 
-def scored_experts(h, W, pre, mlp):
+def scored_experts(h, W, pre, mlp, forced=None, chosen=None):
     """Every token uses the ``top`` experts with the largest sigmoid(router logit); an expert's score multiplies its
-    input, and the scores are not renormalised: out = sum_e expert_e(s_e h)."""
+    input, and the scores are not renormalised: out = sum_e expert_e(s_e h).
+
+    ``forced`` ([T, top] expert indices) replaces the choice (the scores stay this function's own): a comparison with an
+    implementation that rounds differently then does not hang on tokens whose best experts are nearly tied.
+    ``chosen``: a list that receives, per token, (this function's own choice, the margin between the last chosen and
+    the first unchosen score)."""
     E, top, limit = mlp["router"]["experts"], mlp["router"]["top"], float(mlp["expert"]["limit"])
     s = torch.sigmoid(h @ W[pre + "router"].T)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
+        ranked = sorted(range(E), key=lambda e: (-float(s[t, e]), e))
+        order = ranked[:top]
+        if chosen is not None:
+            margin = float(s[t, ranked[top - 1]] - s[t, ranked[top]]) if top < E else float("inf")
+            chosen.append((order, margin))
+        if forced is not None:
+            order = [int(e) for e in forced[t]]
         for e in order:
             out[t] += clamped_expert(s[t, e] * h[t], W, f"{pre}e{e}.", limit)
     return out
@@ -155,9 +166,9 @@ class PlainVilulorn:
         self.W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
         self.eps = float(config["norm"]["eps"])
 
-    def logits(self, tokens, layers_out=None):
+    def logits(self, tokens, layers_out=None, forced=None, chosen=None):
         """[T, vocab] for a whole sequence from position 0; ``layers_out``: a list that receives the stream after
-        every layer."""
+        every layer; ``forced`` {layer: [T, top] expert indices} and ``chosen`` {layer: list}: see ``scored_experts``."""
         W, eps = self.W, self.eps
         x = embed_with_positions(tokens, W, self.dtype)
         kv = {}
@@ -174,7 +185,8 @@ class PlainVilulorn:
                 raise ValueError(L["type"])
             x = x + rms_norm(r, W[f"l{i}.norm1"], eps)
             if L.get("mlp") is not None:
-                x = x + rms_norm(scored_experts(x, W, f"l{i}.mlp.", L["mlp"]), W[f"l{i}.norm2"], eps)
+                x = x + rms_norm(scored_experts(x, W, f"l{i}.mlp.", L["mlp"], None if forced is None else forced.get(i),
+                                                None if chosen is None else chosen.setdefault(i, [])), W[f"l{i}.norm2"], eps)
             if layers_out is not None:
                 layers_out.append(x.clone())
         return rms_norm(x, W["final.norm"], eps) @ W["head"].T
