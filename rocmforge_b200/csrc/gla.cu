@@ -7,16 +7,14 @@
 //
 //   gla_prepare   q (times q_scale), k of the projection's row as float, and alpha = exp(log sigmoid(z) / tau) with
 //                 log sigmoid(z) = min(z, 0) - log1p(exp(-|z|)): float [3, T, heads*dim]
-//   gla_scan      the recurrence, token by token.  The state of a (sequence, head) is kept as [vdim][dim] (a column of
-//                 S, one value dimension, is contiguous), like retention's.  A block owns (sequence, head, a slice of
-//                 value columns); the columns of S are independent of each other, so the slices never talk.  A warp
-//                 owns CPW columns and a lane the rows lane, lane + 32, ... of each in registers, so one load of a
-//                 token's q, k and alpha from shared memory serves CPW columns.  The order of every sum is fixed by
-//                 (dim, position in the sequence) alone: how a prompt is cut into steps, what else is in the batch
-//                 and how many columns a warp holds change no bit.
+//   gla_scan      the recurrence, token by token.  The state of a (sequence, head) is kept as [dim][vdim] (a row of S,
+//                 one key channel, is contiguous).  A block owns (sequence, head, 32 value columns); the columns of S
+//                 are independent of each other, so the blocks never talk.  A lane owns a column, a warp a slice of
+//                 rows.  The order of every sum is fixed by (dim, position in the sequence) alone: how a prompt is cut
+//                 into steps and what else is in the batch change no bit.
 #include "common.cuh"
 
-#define GL_WARPS 8            // warps of a scan block
+#define GL_ROWS 16            // rows of the state (key channels) that a warp of a scan block holds
 #define GL_TOK 16             // tokens staged in shared memory at a time
 
 template <typename T>
@@ -36,139 +34,245 @@ __global__ void gla_prepare_kernel(const T* __restrict__ src, int row_stride, in
     }
 }
 
-// grid (sequence, head, ceil(vdim / (GL_WARPS * CPW))); R = ceil(dim / 32) rows of a column per lane.
-template <typename T, int R, int CPW>
-__global__ void __launch_bounds__(GL_WARPS * 32)
+// grid (sequence, head, ceil(vdim / 32)); a block has ceil(dim / GL_ROWS) warps.  Warp w holds rows w * GL_ROWS .. of the
+// state for the block's 32 value columns, lane l column j0 + l: GL_ROWS state elements per thread, in registers.
+// Per token a thread updates its rows (s = alpha_i s + k_i v_j) and adds up s q_i over them (four partial sums, by
+// i mod 4); q, k and alpha of the token's rows come from shared memory 16 bytes at a time, the same address for all
+// lanes.  The warps' sums for the staged tokens go to shared memory and are added in warp order once per stage:
+// no shuffles, one barrier pair per GL_TOK tokens, and a chain per token that is the state's FMA alone.
+__device__ __forceinline__ void gl_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gl_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// One token for a thread's GL_ROWS rows of one column: s <- a s + k v, returns sum_r s q (four partial sums by r mod 4).
+__device__ __forceinline__ float gl_token(float (&s)[GL_ROWS], const float* __restrict__ a, const float* __restrict__ k,
+                                          const float* __restrict__ q, float vj) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < GL_ROWS; r += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(a + r);
+        const float4 k4 = *reinterpret_cast<const float4*>(k + r);
+        const float4 q4 = *reinterpret_cast<const float4*>(q + r);
+        s[r + 0] = fmaf(a4.x, s[r + 0], k4.x * vj); acc[0] = fmaf(s[r + 0], q4.x, acc[0]);
+        s[r + 1] = fmaf(a4.y, s[r + 1], k4.y * vj); acc[1] = fmaf(s[r + 1], q4.y, acc[1]);
+        s[r + 2] = fmaf(a4.z, s[r + 2], k4.z * vj); acc[2] = fmaf(s[r + 2], q4.z, acc[2]);
+        s[r + 3] = fmaf(a4.w, s[r + 3], k4.w * vj); acc[3] = fmaf(s[r + 3], q4.w, acc[3]);
+    }
+    return (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
+
+// The tokens of a stage are copied into shared memory asynchronously while the stage before is computed (two buffers):
+// with one sequence there are few blocks, and a block that waited for its loads between stages spent half its time so.
+template <typename T>
+__global__ void __launch_bounds__(512)
 gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                 const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
-                const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim) {
-    constexpr int COLS = GL_WARPS * CPW;
-    extern __shared__ float sh[];                     // q, k, alpha [GL_TOK][dim] each, v [GL_TOK][COLS]
-    float* qs = sh;
-    float* ks = qs + GL_TOK * dim;
-    float* as = ks + GL_TOK * dim;
-    float* vs = as + GL_TOK * dim;
+                const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
+    extern __shared__ __align__(16) float sh[];
+    const int warps = blockDim.x >> 5;
+    const int dimP = warps * GL_ROWS;                 // dim rounded up to whole warps; the padding rows are zero
+    const int buf = GL_TOK * dimP;
+    float* qs = sh;                                   // q, k, alpha [2][GL_TOK][dimP] each
+    float* ks = qs + 2 * buf;
+    float* as = ks + 2 * buf;
+    float* vs = as + 2 * buf;                         // v [2][GL_TOK][32]
+    float* part = vs + 2 * GL_TOK * 32;               // the warps' sums [GL_TOK][warps][32]
     pdl_trigger();
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = j0 + lane, i0 = warp * GL_ROWS;
     const int row0 = cu_q[b], row1 = cu_q[b + 1];
     const int slot = seq_slot[b];
     const int width = heads * dim;
-    float* S = state + ((size_t)slot * heads + h) * vdim * dim;
+    float* S = state + ((size_t)slot * heads + h) * dim * vdim;
+    // the padding rows never change: zero once, in both buffers
+    for (int idx = threadIdx.x; idx < 2 * GL_TOK * (dimP - dim); idx += blockDim.x) {
+        const int tt = idx / (dimP - dim), i = dim + idx - tt * (dimP - dim);
+        qs[tt * dimP + i] = 0.f; ks[tt * dimP + i] = 0.f; as[tt * dimP + i] = 0.f;
+    }
     pdl_wait();
-    float s[CPW][R];
+    float s[GL_ROWS];
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) {
-        const int j = j0 + warp * CPW + c;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = lane + 32 * r;
-            s[c][r] = (i < dim && j < vdim) ? S[(size_t)j * dim + i] : 0.f;
-        }
-    }
-    for (int t0 = row0; t0 < row1; t0 += GL_TOK) {
+    for (int r = 0; r < GL_ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
+
+    // asynchronous copies of q, k, alpha of the stage that starts at token t0 into buffer p; the caller commits
+    auto fetch = [&](int t0, int p) {
         const int cnt = min(GL_TOK, row1 - t0);
-        __syncthreads();                              // the tokens before are used up
-        for (int idx = threadIdx.x; idx < cnt * dim; idx += blockDim.x) {
-            const int tt = idx / dim, i = idx - tt * dim;
-            const size_t g = (size_t)(t0 + tt) * width + h * dim + i;
-            qs[idx] = q[g];
-            ks[idx] = k[g];
-            as[idx] = alpha[g];
+        if (vec) {
+            const int d4 = dim >> 2;
+            for (int idx = threadIdx.x; idx < cnt * d4; idx += blockDim.x) {
+                const int tt = idx / d4, i = (idx - tt * d4) << 2;
+                const size_t g = (size_t)(t0 + tt) * width + h * dim + i;
+                const int d = p * buf + tt * dimP + i;
+                gl_copy16(qs + d, q + g); gl_copy16(ks + d, k + g); gl_copy16(as + d, alpha + g);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < cnt * dim; idx += blockDim.x) {
+                const int tt = idx / dim, i = idx - tt * dim;
+                const size_t g = (size_t)(t0 + tt) * width + h * dim + i;
+                const int d = p * buf + tt * dimP + i;
+                gl_copy4(qs + d, q + g); gl_copy4(ks + d, k + g); gl_copy4(as + d, alpha + g);
+            }
         }
-        for (int idx = threadIdx.x; idx < cnt * COLS; idx += blockDim.x) {
-            const int tt = idx / COLS, c = idx - tt * COLS;
-            vs[idx] = (j0 + c < vdim) ? Cvt<T>::to_f32(v[(size_t)(t0 + tt) * v_stride + h * vdim + j0 + c]) : 0.f;
+    };
+    // v of a stage: GL_TOK * 32 values, up to two per thread (blocks have at least 32 threads: then sixteen), through registers
+    auto v_value = [&](int t0, int idx) -> float {
+        const int cnt = min(GL_TOK, row1 - t0);
+        const int tt = idx >> 5, c = idx & 31;
+        return (tt < cnt && j0 + c < vdim) ? Cvt<T>::to_f32(v[(size_t)(t0 + tt) * v_stride + h * vdim + j0 + c]) : 0.f;
+    };
+    if (row0 < row1) {
+        fetch(row0, 0);
+        for (int idx = threadIdx.x; idx < GL_TOK * 32; idx += blockDim.x) vs[idx] = v_value(row0, idx);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int p = 0;
+    for (int t0 = row0; t0 < row1; t0 += GL_TOK, p ^= 1) {
+        const int cnt = min(GL_TOK, row1 - t0);
+        const bool more = t0 + GL_TOK < row1;
+        float v_next[16];                             // GL_TOK * 32 / 32 threads at least
+        if (more) {
+            fetch(t0 + GL_TOK, p ^ 1);
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const int idx = threadIdx.x + u * blockDim.x;
+                v_next[u] = idx < GL_TOK * 32 ? v_value(t0 + GL_TOK, idx) : 0.f;
+            }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");       // this stage's copies have landed (the next one's may fly)
         __syncthreads();
-#pragma unroll 2
-        for (int tt = 0; tt < cnt; ++tt) {
-            float vj[CPW], acc[CPW];
+        const float* qb = qs + p * buf;
+        const float* kb = ks + p * buf;
+        const float* ab = as + p * buf;
+        const float* vb = vs + p * GL_TOK * 32;
+        // A stage's sums stay in registers until all its tokens are done: with no store between the tokens the loads of
+        // the next tokens start under the arithmetic of this one (the chain per token is the state's FMA alone).
+        float sums[GL_TOK];
+        if (cnt == GL_TOK) {
 #pragma unroll
-            for (int c = 0; c < CPW; ++c) { vj[c] = vs[tt * COLS + warp * CPW + c]; acc[c] = 0.f; }
+            for (int tt = 0; tt < GL_TOK; ++tt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * 32 + lane]);
+        } else {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int i = lane + 32 * r;
-                if (i < dim) {
-                    const float a = as[tt * dim + i], kk = ks[tt * dim + i], qq = qs[tt * dim + i];
+            for (int tt = 0; tt < GL_TOK; ++tt)
+                if (tt < cnt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * 32 + lane]);
+        }
 #pragma unroll
-                    for (int c = 0; c < CPW; ++c) {
-                        s[c][r] = fmaf(a, s[c][r], kk * vj[c]);
-                        acc[c] = fmaf(s[c][r], qq, acc[c]);
-                    }
-                }
-            }
+        for (int tt = 0; tt < GL_TOK; ++tt)
+            if (tt < cnt) part[(tt * warps + warp) * 32 + lane] = sums[tt];
+        __syncthreads();                              // the sums are complete; this stage's buffers are used up
+        for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
+            const int tt = idx >> 5, c = idx & 31;
+            float sum = 0.f;
+            for (int w = 0; w < warps; ++w) sum += part[(tt * warps + w) * 32 + c];
+            if (j0 + c < vdim) o[(size_t)(t0 + tt) * heads * vdim + h * vdim + j0 + c] = sum;
+        }
+        if (more) {
 #pragma unroll
-            for (int c = 0; c < CPW; ++c) {
-                const float sum = warp_sum(acc[c]);
-                const int j = j0 + warp * CPW + c;
-                if (lane == 0 && j < vdim) o[(size_t)(t0 + tt) * heads * vdim + h * vdim + j] = sum;
+            for (int u = 0; u < 16; ++u) {
+                const int idx = threadIdx.x + u * blockDim.x;
+                if (idx < GL_TOK * 32) vs[(p ^ 1) * GL_TOK * 32 + idx] = v_next[u];
             }
         }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (j < vdim) {
 #pragma unroll
-    for (int c = 0; c < CPW; ++c) {
-        const int j = j0 + warp * CPW + c;
-        if (j < vdim) {
+        for (int r = 0; r < GL_ROWS; ++r)
+            if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
+    }
+}
+
+// One token per sequence (decoding): the same arithmetic without the staging.  grid (sequence, head, ceil(vdim / 32)),
+// a warp per GL_ROWS rows as above; a thread reads its rows' q, k and alpha straight from global memory (16 bytes at a
+// time where aligned, the same address for all lanes of a warp) and its state elements once, and writes them once.
+template <typename T>
+__global__ void __launch_bounds__(512)
+gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
+                  const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
+                  const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
+    __shared__ float part[16 * 32];
+    pdl_trigger();
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int j = j0 + lane, i0 = warp * GL_ROWS;
+    const int t = cu_q[b];
+    float* S = state + ((size_t)seq_slot[b] * heads + h) * dim * vdim;
+    pdl_wait();
+    float s[GL_ROWS];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int i = lane + 32 * r;
-                if (i < dim) S[(size_t)j * dim + i] = s[c][r];
-            }
+    for (int r = 0; r < GL_ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
+    const size_t g = (size_t)t * heads * dim + (size_t)h * dim + i0;
+    float a[GL_ROWS], kk[GL_ROWS], qq[GL_ROWS];
+    if (vec && i0 + GL_ROWS <= dim) {
+#pragma unroll
+        for (int r = 0; r < GL_ROWS; r += 4) {
+            const float4 a4 = *reinterpret_cast<const float4*>(alpha + g + r);
+            const float4 k4 = *reinterpret_cast<const float4*>(k + g + r);
+            const float4 q4 = *reinterpret_cast<const float4*>(q + g + r);
+            a[r] = a4.x; a[r + 1] = a4.y; a[r + 2] = a4.z; a[r + 3] = a4.w;
+            kk[r] = k4.x; kk[r + 1] = k4.y; kk[r + 2] = k4.z; kk[r + 3] = k4.w;
+            qq[r] = q4.x; qq[r + 1] = q4.y; qq[r + 2] = q4.z; qq[r + 3] = q4.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < GL_ROWS; ++r) {
+            const bool in = i0 + r < dim;
+            a[r] = in ? alpha[g + r] : 0.f; kk[r] = in ? k[g + r] : 0.f; qq[r] = in ? q[g + r] : 0.f;
         }
     }
-}
-
-template <typename T, int R, int CPW>
-static int launch_scan_rc(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
-                          float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim,
-                          cudaStream_t st) {
-    constexpr int COLS = GL_WARPS * CPW;
-    const size_t smem = (size_t)(3 * GL_TOK * dim + GL_TOK * COLS) * sizeof(float);
-    const int gz = (vdim + COLS - 1) / COLS;
-    if (gz > 65535) return RF_ERR_UNSUPPORTED;
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, R, CPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
+    const float vj = j < vdim ? Cvt<T>::to_f32(v[(size_t)t * v_stride + h * vdim + j]) : 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < GL_ROWS; ++r) {               // the same operations in the same order as gl_token
+        s[r] = fmaf(a[r], s[r], kk[r] * vj);
+        acc[r & 3] = fmaf(s[r], qq[r], acc[r & 3]);
     }
-    rf_launch(gla_scan_kernel<T, R, CPW>, dim3(B, heads, gz), dim3(GL_WARPS * 32), smem, st, q, k, alpha,
-              reinterpret_cast<const T*>(v), v_stride, state, o, cu_q, seq_slot, heads, dim, vdim);
-    RF_LAUNCH_CHECK();
-    return 0;
-}
-
-template <typename T, int R>
-static int launch_scan_r(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
-                         float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int sms,
-                         cudaStream_t st) {
-    // columns per warp: as many as still leave about two blocks per SM (a column's arithmetic is the same in all three)
-    const long long groups = (long long)B * heads;
-    if (R <= 4 && groups * ((vdim + 8 * 4 - 1) / (8 * 4)) >= 2LL * sms)
-        return launch_scan_rc<T, R, 4>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, st);
-    if (groups * ((vdim + 8 * 2 - 1) / (8 * 2)) >= 2LL * sms)
-        return launch_scan_rc<T, R, 2>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, st);
-    return launch_scan_rc<T, R, 1>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, st);
+    part[warp * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    if (j < vdim) {
+#pragma unroll
+        for (int r = 0; r < GL_ROWS; ++r)
+            if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
+    }
+    __syncthreads();
+    if (warp == 0 && j < vdim) {
+        float sum = 0.f;
+        for (int w = 0; w < warps; ++w) sum += part[w * 32 + lane];
+        o[(size_t)t * heads * vdim + h * vdim + j] = sum;
+    }
 }
 
 template <typename T>
 static int launch_scan(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
-                       float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int sms,
+                       float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
                        cudaStream_t st) {
     if (B <= 0) return 0;
-    if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535) return RF_ERR_UNSUPPORTED;
-    if (sms <= 0) sms = 148;
-#define GL_CASE(R) return launch_scan_r<T, R>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, sms, st)
-    switch ((dim + 31) / 32) {
-        case 1: GL_CASE(1);
-        case 2: GL_CASE(2);
-        case 3: GL_CASE(3);
-        case 4: GL_CASE(4);
-        case 5: case 6: GL_CASE(6);
-        default: GL_CASE(8);
+    const int warps = (dim + GL_ROWS - 1) / GL_ROWS;
+    const int gz = (vdim + 31) / 32;
+    if (dim <= 0 || warps > 16 || vdim <= 0 || heads <= 0 || heads > 65535 || gz > 65535) return RF_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(6 * GL_TOK * warps * GL_ROWS + 2 * GL_TOK * 32 + GL_TOK * warps * 32) * sizeof(float);
+    // rows of q, k, alpha are copied 16 bytes at a time where a head's slice of every token starts on such a boundary
+    const int vec = dim % 4 == 0 && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                                       reinterpret_cast<uintptr_t>(alpha)) & 15);
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
     }
-#undef GL_CASE
+    if (one_token) {
+        rf_launch(gla_decode_kernel<T>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
+                  v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
+    rf_launch(gla_scan_kernel<T>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
+              v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+    RF_LAUNCH_CHECK();
+    return 0;
 }
 
 template <typename T>
@@ -192,10 +296,12 @@ int rf_gla_prepare(int dtype, const void* src, int row_stride, int q_col, int k_
     return dtype == 0 ? launch_prepare<float>(src, row_stride, q_col, k_col, z, qka, width, q_scale, tau, T_, st)
                       : launch_prepare<__nv_bfloat16>(src, row_stride, q_col, k_col, z, qka, width, q_scale, tau, T_, st);
 }
-// state float [slots, heads, vdim, dim]; o float [T, heads*vdim]; sms: multiprocessors of the device (sizes the blocks)
+// state float [slots, heads, dim, vdim]; o float [T, heads*vdim]; one_token: every sequence of the step brings exactly
+// one token (the kernel without staging; the same bits as the general one)
 int rf_gla_scan(int dtype, const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
-                float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int sms, cudaStream_t st) {
-    return dtype == 0 ? launch_scan<float>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, sms, st)
-                      : launch_scan<__nv_bfloat16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, sms, st);
+                float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
+                cudaStream_t st) {
+    return dtype == 0 ? launch_scan<float>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, st)
+                      : launch_scan<__nv_bfloat16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, st);
 }
 }

@@ -804,22 +804,24 @@ def gla_prepare(proj: torch.Tensor, q_col: int, k_col: int, z: torch.Tensor, hea
 
 
 def gla_scan(qka: torch.Tensor, v: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, seq_slot: torch.Tensor,
-             heads: int, dim: int, vdim: int) -> torch.Tensor:
+             heads: int, dim: int, vdim: int, one_token: bool = False) -> torch.Tensor:
     """S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t, token by token for every sequence of the step; ``qka`` as
-    ``gla_prepare`` leaves it; ``state`` [slots, heads, vdim, dim] float32 (S transposed) is read at the step's start and
-    left as after its last token; ``v`` a [T, heads*vdim] view (rows may be strided).  Returns o float32 [T, heads*vdim]."""
+    ``gla_prepare`` leaves it; ``state`` [slots, heads, dim, vdim] float32 is read at the step's start and
+    left as after its last token; ``v`` a [T, heads*vdim] view (rows may be strided).  ``one_token``: every sequence brings
+    exactly one token (a kernel without staging runs; the same bits).  Returns o float32 [T, heads*vdim]."""
     need_cuda(qka, v, state, cu_q, seq_slot)
     T = qka.shape[1]
     need(qka.dtype == torch.float32 and qka.is_contiguous() and qka.shape == (3, T, heads * dim), "gla_scan: bad q/k/alpha")
     need(v.shape == (T, heads * vdim) and v.stride(1) == 1, "gla_scan: v must be [T, heads*vdim]")
-    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, vdim, dim),
-         "gla_scan: state must be float32 [slots, heads, vdim, dim]")
+    need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+         "gla_scan: state must be float32 [slots, heads, dim, vdim]")
     B = seq_slot.shape[0]
+    need(not one_token or T == B, "gla_scan: one_token means one token for every sequence")
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qka.device)
     f = _f("gla", "rf_gla_scan", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
            c_int, c_int, c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(v.dtype), ptr(qka[0]), ptr(qka[1]), ptr(qka[2]), ptr(v), v.stride(0), ptr(state), ptr(o), ptr(cu_q),
-            ptr(seq_slot), B, heads, dim, vdim, device_sm_count(qka.device), stream()),
+            ptr(seq_slot), B, heads, dim, vdim, int(one_token), stream()),
           f"gla_scan (heads={heads}, dim={dim}, vdim={vdim})")
     return o
 

@@ -24,8 +24,7 @@ class GatedLinearAttention(Mixer):
 
     The projections run in the compute dtype, as one product q | k | v | g | a1 (W_a1 is the narrow first half of the
     decay's low-rank projection) and a second, small one for z, whose result stays 32-bit; q, k, the decay (formed as
-    exp(log sigmoid(z) / tau)), the state, o and its norm are 32-bit.  The state is kept as [heads, vdim, dim], like
-    retention's.  ``names``: the tensors' names below the part's prefix (keys q, k, v, g, o, a1, a2, a2_bias, norm).
+    exp(log sigmoid(z) / tau)), the state, o and its norm are 32-bit.  The state is kept as [heads, dim, vdim].  ``names``: the tensors' names below the part's prefix (keys q, k, v, g, o, a1, a2, a2_bias, norm).
     """
 
     def __init__(self, hidden: int, n_heads: int, dim: int, vdim: int, tau: float, eps: float, *, decay_rank: int,
@@ -83,7 +82,7 @@ class GatedLinearAttention(Mixer):
         return ["elementwise", "retention", "gla"]
 
     def cache_request(self):
-        return StateRequest.of(S=((self.n_heads, self.vdim, self.dim), torch.float32))
+        return StateRequest.of(S=((self.n_heads, self.dim, self.vdim), torch.float32))
 
     def gated(self, ctx, y, state_view):
         """The gated, normed heads [T, heads*vdim] in the compute dtype (the output product's input)."""
@@ -94,7 +93,8 @@ class GatedLinearAttention(Mixer):
         qka = kernels.gla_prepare(p, 0, self.qk_size, z, self.n_heads, self.dim, self.q_scale, self.tau)
         v = p[:, 2 * self.qk_size: 2 * self.qk_size + self.v_size]
         g = p[:, 2 * self.qk_size + self.v_size: 2 * self.qk_size + 2 * self.v_size]
-        o = kernels.gla_scan(qka, v, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.dim, self.vdim)
+        o = kernels.gla_scan(qka, v, state_view["S"], ctx.cu_q, ctx.seq_slot, self.n_heads, self.dim, self.vdim,
+                             one_token=ctx.is_decode)
         return kernels.retention_gate(o, g, self.n_heads, self.vdim, self.eps, weight=self.norm_w)
 
     def forward(self, ctx, y, cache_view, stream):
