@@ -34,8 +34,11 @@ __global__ void gla_prepare_kernel(const T* __restrict__ src, int row_stride, in
     }
 }
 
-// grid (sequence, head, ceil(vdim / 32)); a block has ceil(dim / GL_ROWS) warps.  Warp w holds rows w * GL_ROWS .. of the
-// state for the block's 32 value columns, lane l column j0 + l: GL_ROWS state elements per thread, in registers.
+// grid (sequence, head, ceil(vdim / COLS)); the rows of the state are cut into slices of GL_ROWS.  With COLS = 32 a warp
+// holds one slice for the block's 32 value columns, lane l column j0 + l; with COLS = 16 (taken when the step has too few
+// (sequence, head) pairs to give every SM a block of 32 columns) a warp holds two slices side by side for 16 columns.
+// Either way a thread has GL_ROWS state elements of one column in registers, and a column's arithmetic (slices of the
+// same rows, added in the same order) is the same, so the choice changes no bit.
 // Per token a thread updates its rows (s = alpha_i s + k_i v_j) and adds up s q_i over them (four partial sums, by
 // i mod 4); q, k and alpha of the token's rows come from shared memory 16 bytes at a time, the same address for all
 // lanes.  The warps' sums for the staged tokens go to shared memory and are added in warp order once per stage:
@@ -66,24 +69,26 @@ __device__ __forceinline__ float gl_token(float (&s)[GL_ROWS], const float* __re
 
 // The tokens of a stage are copied into shared memory asynchronously while the stage before is computed (two buffers):
 // with one sequence there are few blocks, and a block that waited for its loads between stages spent half its time so.
-template <typename T>
+template <typename T, int COLS>
 __global__ void __launch_bounds__(512)
 gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                 const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
                 const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
     extern __shared__ __align__(16) float sh[];
-    const int warps = blockDim.x >> 5;
-    const int dimP = warps * GL_ROWS;                 // dim rounded up to whole warps; the padding rows are zero
+    constexpr int SPW = 32 / COLS;                    // row slices side by side in a warp
+    const int slices = (blockDim.x >> 5) * SPW;
+    const int dimP = slices * GL_ROWS;                // dim rounded up to whole slices; the padding rows are zero
     const int buf = GL_TOK * dimP;
     float* qs = sh;                                   // q, k, alpha [2][GL_TOK][dimP] each
     float* ks = qs + 2 * buf;
     float* as = ks + 2 * buf;
-    float* vs = as + 2 * buf;                         // v [2][GL_TOK][32]
-    float* part = vs + 2 * GL_TOK * 32;               // the warps' sums [GL_TOK][warps][32]
+    float* vs = as + 2 * buf;                         // v [2][GL_TOK][COLS]
+    float* part = vs + 2 * GL_TOK * COLS;             // the slices' sums [GL_TOK][slices][COLS]
     pdl_trigger();
-    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
+    const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int j = j0 + lane, i0 = warp * GL_ROWS;
+    const int col = lane % COLS, slice = warp * SPW + lane / COLS;
+    const int j = j0 + col, i0 = slice * GL_ROWS;
     const int row0 = cu_q[b], row1 = cu_q[b + 1];
     const int slot = seq_slot[b];
     const int width = heads * dim;
@@ -118,28 +123,28 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
             }
         }
     };
-    // v of a stage: GL_TOK * 32 values, up to two per thread (blocks have at least 32 threads: then sixteen), through registers
+    // v of a stage: GL_TOK * COLS values, up to sixteen per thread (a block has at least 32 threads), through registers
     auto v_value = [&](int t0, int idx) -> float {
         const int cnt = min(GL_TOK, row1 - t0);
-        const int tt = idx >> 5, c = idx & 31;
+        const int tt = idx / COLS, c = idx % COLS;
         return (tt < cnt && j0 + c < vdim) ? Cvt<T>::to_f32(v[(size_t)(t0 + tt) * v_stride + h * vdim + j0 + c]) : 0.f;
     };
     if (row0 < row1) {
         fetch(row0, 0);
-        for (int idx = threadIdx.x; idx < GL_TOK * 32; idx += blockDim.x) vs[idx] = v_value(row0, idx);
+        for (int idx = threadIdx.x; idx < GL_TOK * COLS; idx += blockDim.x) vs[idx] = v_value(row0, idx);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     int p = 0;
     for (int t0 = row0; t0 < row1; t0 += GL_TOK, p ^= 1) {
         const int cnt = min(GL_TOK, row1 - t0);
         const bool more = t0 + GL_TOK < row1;
-        float v_next[16];                             // GL_TOK * 32 / 32 threads at least
+        float v_next[16];                             // GL_TOK * COLS / 32 threads at least
         if (more) {
             fetch(t0 + GL_TOK, p ^ 1);
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
                 const int idx = threadIdx.x + u * blockDim.x;
-                v_next[u] = idx < GL_TOK * 32 ? v_value(t0 + GL_TOK, idx) : 0.f;
+                v_next[u] = idx < GL_TOK * COLS ? v_value(t0 + GL_TOK, idx) : 0.f;
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -148,33 +153,33 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         const float* qb = qs + p * buf;
         const float* kb = ks + p * buf;
         const float* ab = as + p * buf;
-        const float* vb = vs + p * GL_TOK * 32;
+        const float* vb = vs + p * GL_TOK * COLS;
         // A stage's sums stay in registers until all its tokens are done: with no store between the tokens the loads of
         // the next tokens start under the arithmetic of this one (the chain per token is the state's FMA alone).
         float sums[GL_TOK];
         if (cnt == GL_TOK) {
 #pragma unroll
-            for (int tt = 0; tt < GL_TOK; ++tt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * 32 + lane]);
+            for (int tt = 0; tt < GL_TOK; ++tt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col]);
         } else {
 #pragma unroll
             for (int tt = 0; tt < GL_TOK; ++tt)
-                if (tt < cnt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * 32 + lane]);
+                if (tt < cnt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col]);
         }
 #pragma unroll
         for (int tt = 0; tt < GL_TOK; ++tt)
-            if (tt < cnt) part[(tt * warps + warp) * 32 + lane] = sums[tt];
+            if (tt < cnt) part[(tt * slices + slice) * COLS + col] = sums[tt];
         __syncthreads();                              // the sums are complete; this stage's buffers are used up
-        for (int idx = threadIdx.x; idx < cnt * 32; idx += blockDim.x) {
-            const int tt = idx >> 5, c = idx & 31;
+        for (int idx = threadIdx.x; idx < cnt * COLS; idx += blockDim.x) {
+            const int tt = idx / COLS, c = idx % COLS;
             float sum = 0.f;
-            for (int w = 0; w < warps; ++w) sum += part[(tt * warps + w) * 32 + c];
+            for (int w = 0; w < slices; ++w) sum += part[(tt * slices + w) * COLS + c];
             if (j0 + c < vdim) o[(size_t)(t0 + tt) * heads * vdim + h * vdim + j0 + c] = sum;
         }
         if (more) {
 #pragma unroll
             for (int u = 0; u < 16; ++u) {
                 const int idx = threadIdx.x + u * blockDim.x;
-                if (idx < GL_TOK * 32) vs[(p ^ 1) * GL_TOK * 32 + idx] = v_next[u];
+                if (idx < GL_TOK * COLS) vs[(p ^ 1) * GL_TOK * COLS + idx] = v_next[u];
             }
         }
     }
@@ -245,34 +250,49 @@ gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     }
 }
 
+template <typename T, int COLS>
+static int launch_scan_cols(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
+                            float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int vec,
+                            cudaStream_t st) {
+    constexpr int SPW = 32 / COLS;
+    const int slices = ((dim + GL_ROWS - 1) / GL_ROWS + SPW - 1) / SPW * SPW;
+    const int warps = slices / SPW;
+    const int gz = (vdim + COLS - 1) / COLS;
+    if (gz > 65535) return RF_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(6 * GL_TOK * slices * GL_ROWS + 2 * GL_TOK * COLS + GL_TOK * slices * COLS) * sizeof(float);
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = smem;
+    }
+    rf_launch(gla_scan_kernel<T, COLS>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
+              v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 template <typename T>
 static int launch_scan(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                        float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
-                       cudaStream_t st) {
+                       int sms, cudaStream_t st) {
     if (B <= 0) return 0;
     const int warps = (dim + GL_ROWS - 1) / GL_ROWS;
     const int gz = (vdim + 31) / 32;
     if (dim <= 0 || warps > 16 || vdim <= 0 || heads <= 0 || heads > 65535 || gz > 65535) return RF_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(6 * GL_TOK * warps * GL_ROWS + 2 * GL_TOK * 32 + GL_TOK * warps * 32) * sizeof(float);
     // rows of q, k, alpha are copied 16 bytes at a time where a head's slice of every token starts on such a boundary
     const int vec = dim % 4 == 0 && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                                        reinterpret_cast<uintptr_t>(alpha)) & 15);
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
     if (one_token) {
         rf_launch(gla_decode_kernel<T>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
                   v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
         RF_LAUNCH_CHECK();
         return 0;
     }
-    rf_launch(gla_scan_kernel<T>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
-              v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
-    RF_LAUNCH_CHECK();
-    return 0;
+    if (sms <= 0) sms = 148;
+    if ((long long)B * heads * gz < sms)              // few blocks: narrower ones, twice as many
+        return launch_scan_cols<T, 16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
+    return launch_scan_cols<T, 32>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
 }
 
 template <typename T>
@@ -298,10 +318,11 @@ int rf_gla_prepare(int dtype, const void* src, int row_stride, int q_col, int k_
 }
 // state float [slots, heads, dim, vdim]; o float [T, heads*vdim]; one_token: every sequence of the step brings exactly
 // one token (the kernel without staging; the same bits as the general one)
+// sms: multiprocessors of the device (sizes the blocks)
 int rf_gla_scan(int dtype, const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
-                float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
+                float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token, int sms,
                 cudaStream_t st) {
-    return dtype == 0 ? launch_scan<float>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, st)
-                      : launch_scan<__nv_bfloat16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, st);
+    return dtype == 0 ? launch_scan<float>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st)
+                      : launch_scan<__nv_bfloat16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
 }
 }

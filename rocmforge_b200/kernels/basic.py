@@ -819,9 +819,9 @@ def gla_scan(qka: torch.Tensor, v: torch.Tensor, state: torch.Tensor, cu_q: torc
     need(not one_token or T == B, "gla_scan: one_token means one token for every sequence")
     o = torch.empty((T, heads * vdim), dtype=torch.float32, device=qka.device)
     f = _f("gla", "rf_gla_scan", c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_int, c_int, c_int, c_int, c_int, c_void_p)
+           c_int, c_int, c_int, c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(v.dtype), ptr(qka[0]), ptr(qka[1]), ptr(qka[2]), ptr(v), v.stride(0), ptr(state), ptr(o), ptr(cu_q),
-            ptr(seq_slot), B, heads, dim, vdim, int(one_token), stream()),
+            ptr(seq_slot), B, heads, dim, vdim, int(one_token), device_sm_count(qka.device), stream()),
           f"gla_scan (heads={heads}, dim={dim}, vdim={vdim})")
     return o
 
