@@ -9,7 +9,7 @@
 //                 (tiles[0] = number of tiles, then (expert, first row, end row) per tile; a tile never spans experts)
 //   moe_combine   out[t] = sum over the token's choices, in the order of the choices, of weight * expert output row
 //                 (no weights: the plain sum, for designs whose weights went into the experts' inputs)
-//   moe_scale_gather / moe_pair_weights   the sorted rows times their pair's weight; the weights in sorted order
+//   (moe_sort can also leave the pairs' weights in the order of the sorted rows, for designs that weight an expert's input)
 // A row of the grouped product depends on its own token alone, so where the sort puts a pair changes no bit.
 #include "common.cuh"
 
@@ -55,7 +55,8 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
 // One block.  counts/cursors live in shared memory (E <= 1024).
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ idx, int n, int E, int BM, int* __restrict__ perm, int* __restrict__ inv,
-                int* __restrict__ offsets, int* __restrict__ tiles, int max_tiles) {
+                int* __restrict__ offsets, int* __restrict__ tiles, int max_tiles, const float* __restrict__ w,
+                float* __restrict__ w_sorted) {
     __shared__ int counts[1024];
     __shared__ int cursor[1024];
     pdl_trigger();
@@ -85,6 +86,7 @@ moe_sort_kernel(const int* __restrict__ idx, int n, int E, int BM, int* __restri
         const int r = atomicAdd(&cursor[idx[i]], 1);
         perm[r] = i;
         inv[i] = r;
+        if (w_sorted != nullptr) w_sorted[r] = w[i];     // the pairs' weights in sorted order, for a product that reads them by row
     }
 }
 
@@ -117,46 +119,7 @@ __global__ void moe_gather_kernel(const uint8_t* __restrict__ x, long long x_str
     }
 }
 
-// out[r, :] = x[perm[r] / top, :] * w[perm[r]] in the dtype of x (the product is formed in 32-bit): the input of an
-// expert whose routing weight multiplies what goes in instead of what comes out
-template <typename T>
-__global__ void moe_scale_gather_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ perm,
-                                        const float* __restrict__ w, int top, T* __restrict__ out, int K) {
-    pdl_trigger();
-    pdl_wait();
-    const int r = blockIdx.x, pair = perm[r];
-    const float sc = w[pair];
-    const T* src = x + (size_t)(pair / top) * x_stride;
-    for (int i = threadIdx.x; i < K; i += blockDim.x) out[(size_t)r * K + i] = Cvt<T>::from_f32(Cvt<T>::to_f32(src[i]) * sc);
-}
-
-// ws[r] = w[perm[r]]: the pairs' weights in sorted order (a grouped product's epilogue reads them by row)
-__global__ void moe_pair_weights_kernel(const int* __restrict__ perm, const float* __restrict__ w, float* __restrict__ ws, int n) {
-    pdl_trigger();
-    pdl_wait();
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r < n) ws[r] = w[perm[r]];
-}
-
 extern "C" {
-int rf_moe_scale_gather(int dtype, const void* x, long long x_stride, const int* perm, const float* w, int top, void* out,
-                        int K, int n, cudaStream_t st) {
-    if (n <= 0 || K <= 0) return 0;
-    if (dtype == 0)
-        rf_launch(moe_scale_gather_kernel<float>, dim3(n), dim3(128), 0, st, reinterpret_cast<const float*>(x), x_stride, perm, w,
-                  top, reinterpret_cast<float*>(out), K);
-    else
-        rf_launch(moe_scale_gather_kernel<__nv_bfloat16>, dim3(n), dim3(128), 0, st, reinterpret_cast<const __nv_bfloat16*>(x),
-                  x_stride, perm, w, top, reinterpret_cast<__nv_bfloat16*>(out), K);
-    RF_LAUNCH_CHECK();
-    return 0;
-}
-int rf_moe_pair_weights(const int* perm, const float* w, float* ws, int n, cudaStream_t st) {
-    if (n <= 0) return 0;
-    rf_launch(moe_pair_weights_kernel, dim3((n + 255) / 256), dim3(256), 0, st, perm, w, ws, n);
-    RF_LAUNCH_CHECK();
-    return 0;
-}
 int rf_moe_gather(const void* x, long long x_stride_bytes, const int* perm, int top, void* out, int row_bytes, int n,
                   cudaStream_t st) {
     if (n <= 0 || row_bytes <= 0) return 0;
@@ -182,13 +145,22 @@ int rf_moe_route(const float* logits, int E, int top, int* idx, float* w, int T_
 int rf_moe_route_scored(const float* logits, int E, int top, int* idx, float* w, int T_, int scoring, cudaStream_t st) {
     return route(logits, E, top, idx, w, T_, scoring, st);
 }
-int rf_moe_sort(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
-                cudaStream_t st) {
+static int sort_pairs(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
+                      const float* w, float* w_sorted, cudaStream_t st) {
     if (n <= 0) return 0;
-    if (E < 1 || E > 1024 || BM < 1) return RF_ERR_UNSUPPORTED;
-    rf_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, st, idx, n, E, BM, perm, inv, offsets, tiles, max_tiles);
+    if (E < 1 || E > 1024 || BM < 1 || ((w == nullptr) != (w_sorted == nullptr))) return RF_ERR_UNSUPPORTED;
+    rf_launch(moe_sort_kernel, dim3(1), dim3(1024), 0, st, idx, n, E, BM, perm, inv, offsets, tiles, max_tiles, w, w_sorted);
     RF_LAUNCH_CHECK();
     return 0;
+}
+int rf_moe_sort(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
+                cudaStream_t st) {
+    return sort_pairs(idx, n, E, BM, perm, inv, offsets, tiles, max_tiles, nullptr, nullptr, st);
+}
+// The same, and w_sorted[r] = w[perm[r]] (float [n]): the pairs' weights in the order of the sorted rows.
+int rf_moe_sort_w(const int* idx, int n, int E, int BM, int* perm, int* inv, int* offsets, int* tiles, int max_tiles,
+                  const float* w, float* w_sorted, cudaStream_t st) {
+    return sort_pairs(idx, n, E, BM, perm, inv, offsets, tiles, max_tiles, w, w_sorted, st);
 }
 int rf_moe_combine(const float* y, const int* inv, const float* w, float* out, int top, int H, int T_, cudaStream_t st) {
     const size_t n = (size_t)T_ * H;

@@ -6,7 +6,6 @@ from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, 
                     attention_prefill_tc, attention_prefill_tc_supported, PREFILL_TC_TILE)
 from .basic import (relu2, add_row, branch_norm_add, head_norm_kv_write, gemm_simt_grouped, retention_prepare,
                     retention_scan, retention_gate, retention_chunked, RETENTION_CHUNK, moe_route, moe_sort, moe_combine, moe_gather, MOE_TILE_SMALL, MOE_TILE_LARGE, MOE_TILE_TC)
-from .basic import (embed_positions, round_rows, clamped_glu, sigmoid_gate, key_span, gla_prepare, gla_scan, moe_scale_gather,
-                    moe_pair_weights, MOE_SCORINGS)
+from .basic import (embed_positions, round_rows, clamped_glu, sigmoid_gate, key_span, gla_prepare, gla_scan, MOE_SCORINGS)
 from ._ffi import launch_count
 from . import tensor_core

@@ -861,35 +861,11 @@ def moe_route(logits: torch.Tensor, top: int, scoring: str = "softmax_of_chosen"
     return idx, w
 
 
-def moe_scale_gather(x: torch.Tensor, perm: torch.Tensor, w: torch.Tensor, top: int) -> torch.Tensor:
-    """out[r] = x[perm[r] // top] * w.flat[perm[r]] in the dtype of x: the tokens' activations in sorted order, each times
-    the weight of its (token, choice) pair."""
-    need_cuda(x, perm, w)
-    need(x.dim() == 2 and x.stride(1) == 1 and perm.dtype == torch.int32 and w.dtype == torch.float32 and w.is_contiguous()
-         and w.numel() == perm.numel(), "moe_scale_gather: x [T, K], an int32 permutation and float32 weights of its length")
-    n, K = perm.numel(), x.shape[1]
-    out = torch.empty((n, K), dtype=x.dtype, device=x.device)
-    f = _f("moe", "rf_moe_scale_gather", c_int, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p)
-    check(f(dtype_code(x.dtype), ptr(x), x.stride(0), ptr(perm), ptr(w), top, ptr(out), K, n, stream()), "moe_scale_gather")
-    return out
-
-
-def moe_pair_weights(perm: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """w.flat[perm[r]]: the pairs' weights in sorted order, float32 [n]."""
-    need_cuda(perm, w)
-    need(perm.dtype == torch.int32 and w.dtype == torch.float32 and w.is_contiguous() and w.numel() == perm.numel(),
-         "moe_pair_weights: an int32 permutation and float32 weights of its length")
-    n = perm.numel()
-    ws = torch.empty((n,), dtype=torch.float32, device=w.device)
-    f = _f("moe", "rf_moe_pair_weights", c_void_p, c_void_p, c_void_p, c_int, c_void_p)
-    check(f(ptr(perm), ptr(w), ptr(ws), n, stream()), "moe_pair_weights")
-    return ws
-
-
-def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int):
+def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int, weights: torch.Tensor | None = None):
     """The (token, choice) pairs sorted by expert, on the device: (perm [n], inv [n], tiles, max_tiles); the tile table
-    lists (expert, first sorted row, end row) for row tiles of at most ``tile_rows`` rows that never span two experts."""
-    need_cuda(idx)
+    lists (expert, first sorted row, end row) for row tiles of at most ``tile_rows`` rows that never span two experts.
+    With ``weights`` (float32, one per pair) a fifth result: the weights in the order of the sorted rows, float32 [n]."""
+    need_cuda(idx, weights)
     n = idx.numel()
     max_tiles = (n + tile_rows - 1) // tile_rows + n_experts
     dev = idx.device
@@ -897,6 +873,14 @@ def moe_sort(idx: torch.Tensor, n_experts: int, tile_rows: int):
     inv = torch.empty((n,), dtype=torch.int32, device=dev)
     offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
     tiles = torch.empty((1 + 3 * max_tiles,), dtype=torch.int32, device=dev)
+    if weights is not None:
+        need(weights.dtype == torch.float32 and weights.is_contiguous() and weights.numel() == n, "moe_sort: one float32 weight per pair")
+        ws = torch.empty((n,), dtype=torch.float32, device=dev)
+        f = _f("moe", "rf_moe_sort_w", c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+               c_void_p, c_void_p)
+        check(f(ptr(idx), n, n_experts, tile_rows, ptr(perm), ptr(inv), ptr(offsets), ptr(tiles), max_tiles, ptr(weights), ptr(ws),
+                stream()), f"moe_sort (E={n_experts})")
+        return perm, inv, tiles, max_tiles, ws
     f = _f("moe", "rf_moe_sort", c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
     check(f(ptr(idx), n, n_experts, tile_rows, ptr(perm), ptr(inv), ptr(offsets), ptr(tiles), max_tiles, stream()),
           f"moe_sort (E={n_experts})")

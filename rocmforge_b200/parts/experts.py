@@ -115,8 +115,10 @@ class RoutedExperts(FeedForward):
                   and tc.grouped_supported(2 * self.intermediate, self.hidden, tc.CLAMPGLU)
                   and tc.grouped_supported(self.hidden, self.intermediate, tc.F32))
         rows = kernels.MOE_TILE_TC if use_tc else (kernels.MOE_TILE_SMALL if n <= 16 * self.n_experts else kernels.MOE_TILE_LARGE)
-        perm, inv, tiles, max_tiles = kernels.moe_sort(idx, self.n_experts, rows)
-        ws = kernels.moe_pair_weights(perm, w) if on_input else None
+        if on_input:                                  # the sort leaves the pairs' weights in the order of the sorted rows
+            perm, inv, tiles, max_tiles, ws = kernels.moe_sort(idx, self.n_experts, rows, weights=w)
+        else:
+            (perm, inv, tiles, max_tiles), ws = kernels.moe_sort(idx, self.n_experts, rows), None
         if use_tc and self.activation == "clamped_glu":
             # the scale and the activation happen in the first product's epilogue, on its 32-bit sums
             a = tc.gemm_tc_grouped(kernels.moe_gather(y, perm, self.top), self.gate_up, tiles, max_tiles, mode=tc.CLAMPGLU,

@@ -223,7 +223,23 @@ VILULORN_C = dict(seed=23, architecture="Vilulorn", vocab=300, width=256, max_po
                                            mlp=_scored(128, 3, 1, 1.0)),
                           _chunk_attention(heads=8, kv_heads=2, dim=64, vdim=64, chunk=130, scale=0.2, rot_dims=32, rot_base=1e6,
                                            scaling=(4.0, 1.0, 4.0, 256), kv_from=1, mlp=_scored(64, 4, 4, 2.0))])
-VILULORN_CONFIGS = {"VA": VILULORN_A, "VB": VILULORN_B, "VC": VILULORN_C}
+# Two more at the edges of what the kernels take: a width that is no multiple of 8 (no operand of a product is aligned for
+# the tensor-core kernels), sixteen query heads on one kv head (more than the clustered decode attention serves), a state
+# of 256 key channels by 8 value columns and one of 16 by 200, a decay projection of rank 1, 64-element keys with
+# 128-element values, chunks of 2.
+VILULORN_D = dict(seed=24, architecture="Vilulorn", vocab=130, width=100, max_positions=300, norm={"eps": 1e-6}, ranks={1: 1},
+                  layers=[_chunk_attention(heads=16, kv_heads=1, dim=64, vdim=64, chunk=50, scale=0.125, rot_dims=64, rot_base=1e4,
+                                           mlp=_scored(24, 2, 1, 3.0)),
+                          _gla(heads=1, dim=256, vdim=8, tau=32.0, mlp=None),
+                          _chunk_attention(heads=16, kv_heads=1, dim=64, vdim=64, chunk=50, scale=0.2, rot_dims=64, rot_base=1e4,
+                                           kv_from=0, mlp=_scored(16, 3, 2, 1.0))])
+VILULORN_E = dict(seed=25, architecture="Vilulorn", vocab=150, width=128, max_positions=300, norm={"eps": 1e-5}, ranks={2: 24},
+                  layers=[_chunk_attention(heads=16, kv_heads=1, dim=64, vdim=64, chunk=70, scale=0.125, rot_dims=2, rot_base=10.0,
+                                           mlp=_scored(32, 4, 2, 2.0)),
+                          _chunk_attention(heads=2, kv_heads=2, dim=64, vdim=128, chunk=2, scale=0.3, rot_dims=16, rot_base=1e3,
+                                           scaling=(2.0, 1.0, 2.0, 16), mlp=None),
+                          _gla(heads=2, dim=16, vdim=200, tau=0.5, mlp=_scored(8, 9, 4, 0.25))])
+VILULORN_CONFIGS = {"VA": VILULORN_A, "VB": VILULORN_B, "VC": VILULORN_C, "VD": VILULORN_D, "VE": VILULORN_E}
 
 
 def vilulorn_config(cfg: dict):

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import ROOT, VILULORN_CONFIGS, TraceRun, assert_logits_close, random_tokens
+from helpers import ROOT, VILULORN_CONFIGS, TraceRun, random_tokens
 from plain import vilulorn_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -55,12 +55,19 @@ def row_errors(got, ref):
 
 
 def close(got, ref, dtype, what):
-    """float32: element by element.  bfloat16 (with the experts' choice agreed, see ``routed_like_the_engine``): rows
+    """float32: element by element (6e-5 + 3e-4 |reference|).  bfloat16 (with the experts' choice agreed, see ``routed_like_the_engine``): rows
     within 2.5 % on average by the root mean square of their difference, and none beyond 15 %: every layer norms its
     sub-layers' outputs to unit size, which carries one layer's rounding at full size into the next, and blows the
     rounding of a sub-layer's output up where that output happens to be small."""
     if dtype == "float32":
-        return assert_logits_close(got, ref, dtype, what)
+        # three times the other models' bound: an out-norm divides a sub-layer's output by its size, and where that output
+        # is small (experts whose clamped halves nearly cancel) the 32-bit rounding of its sums is divided with it
+        g = torch.as_tensor(np.asarray(got), dtype=torch.float64)
+        r = torch.as_tensor(np.asarray(ref), dtype=torch.float64)
+        assert g.shape == r.shape and torch.isfinite(g).all(), what
+        bad = (g - r).abs() > 6e-5 + 3e-4 * r.abs()
+        assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} logits differ, max diff {float((g - r).abs().max()):.3g}"
+        return
     err = row_errors(got, ref)
     assert float(err.mean()) < 0.025 and float(err.max()) < 0.15, \
         f"{what}: row errors up to {float(err.max()):.3f} (row {int(err.argmax())}), mean {float(err.mean()):.3f}"
@@ -123,7 +130,7 @@ def poison_free_pages(cache):
 # --------------------------------------------------------------------------- the model in the engine
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["VA", "VB", "VC"])
+@pytest.mark.parametrize("name", ["VA", "VB", "VC", "VD", "VE"])
 def test_whole_prompt(folders, name, dtype, monkeypatch):
     """Every position of a prompt that crosses four page borders and every chunk edge of the configuration."""
     from rocmforge_b200 import StepRequest
@@ -156,7 +163,7 @@ def test_token_by_token_from_the_first_token(folders, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["VA", "VB", "VC"])
+@pytest.mark.parametrize("name", ["VA", "VB", "VC", "VD", "VE"])
 def test_portions_of_many_sizes(folders, name, dtype, monkeypatch):
     """A prompt cut into portions of 1 to 70 tokens: the state is carried from step to step, and chunks are counted from
     the sequence's first position, not from where a portion starts."""
@@ -192,7 +199,7 @@ def alone(m, tokens, n_prompt):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["VA", "VC"])
+@pytest.mark.parametrize("name", ["VA", "VC", "VD", "VE"])
 def test_ragged_batch_then_decoding_with_slots_used_again(folders, name, dtype):
     """Unequal prompts in one step, decoded together; requests end at different steps, their slots (state!) and pages go
     to new requests; every request must equal itself alone: the plain model's logits on the 32-bit path; on the bfloat16
