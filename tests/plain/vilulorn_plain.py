@@ -141,15 +141,18 @@ def scored_experts(h, W, pre, mlp, forced=None, chosen=None):
     ``forced`` ([T, top] expert indices) replaces the choice (the scores stay this function's own): a comparison with an
     implementation that rounds differently then does not hang on tokens whose best experts are nearly tied.
     ``chosen``: a list that receives, per token, (this function's own choice, the margin between the last chosen and
-    the first unchosen score)."""
+    the first unchosen logit as a share of the logits' spread)."""
     E, top, limit = mlp["router"]["experts"], mlp["router"]["top"], float(mlp["expert"]["limit"])
-    s = torch.sigmoid(h @ W[pre + "router"].T)
+    z = h @ W[pre + "router"].T
+    s = torch.sigmoid(z)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        ranked = sorted(range(E), key=lambda e: (-float(s[t, e]), e))
+        # ranked by the logits: the sigmoid keeps their order, but far out it rounds to exactly 1 and would make ties
+        ranked = sorted(range(E), key=lambda e: (-float(z[t, e]), e))
         order = ranked[:top]
         if chosen is not None:
-            margin = float(s[t, ranked[top - 1]] - s[t, ranked[top]]) if top < E else float("inf")
+            spread = float(z[t].max() - z[t].min()) + 1e-9
+            margin = float(z[t, ranked[top - 1]] - z[t, ranked[top]]) / spread if top < E else float("inf")
             chosen.append((order, margin))
         if forced is not None:
             order = [int(e) for e in forced[t]]

@@ -79,7 +79,7 @@ class routed_like_the_engine:
     the recurrent state so are, a little, all rows after it.  So the comparison is done in two halves.  Inside this
     context every choice of the engine's router is recorded (``kernels.moe_route`` is wrapped); ``logits`` then runs the
     plain model with those choices forced on it (the scores stay its own) and checks that the engine's choices are the
-    plain model's own wherever the plain model's margin is not small."""
+    plain model's own wherever the plain model's margin (2 % of the logits' spread) is not small."""
 
     def __init__(self, monkeypatch):
         from rocmforge_b200 import kernels
