@@ -14,8 +14,8 @@
 //                 into steps and what else is in the batch change no bit.
 #include "common.cuh"
 
-#define GL_ROWS 16            // rows of the state (key channels) that a warp of a scan block holds
 #define GL_TOK 16             // tokens staged in shared memory at a time
+#define GL_SLICE 8            // rows of the state whose products with q are added up together: the unit of every kernel's sums
 
 template <typename T>
 __global__ void gla_prepare_kernel(const T* __restrict__ src, int row_stride, int q_col, int k_col,
@@ -34,10 +34,10 @@ __global__ void gla_prepare_kernel(const T* __restrict__ src, int row_stride, in
     }
 }
 
-// grid (sequence, head, ceil(vdim / COLS)); the rows of the state are cut into slices of GL_ROWS.  With COLS = 32 a warp
+// grid (sequence, head, ceil(vdim / COLS)); the rows of the state are cut into slices of ROWS (8 or 16, by dim).  With COLS = 32 a warp
 // holds one slice for the block's 32 value columns, lane l column j0 + l; with COLS = 16 (taken when the step has too few
 // (sequence, head) pairs to give every SM a block of 32 columns) a warp holds two slices side by side for 16 columns.
-// Either way a thread has GL_ROWS state elements of one column in registers, and a column's arithmetic (slices of the
+// Either way a thread has ROWS state elements of one column in registers, and a column's arithmetic (slices of the
 // same rows, added in the same order) is the same, so the choice changes no bit.
 // Per token a thread updates its rows (s = alpha_i s + k_i v_j) and adds up s q_i over them (four partial sums, by
 // i mod 4); q, k and alpha of the token's rows come from shared memory 16 bytes at a time, the same address for all
@@ -50,26 +50,31 @@ __device__ __forceinline__ void gl_copy4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// One token for a thread's GL_ROWS rows of one column: s <- a s + k v, returns sum_r s q (four partial sums by r mod 4).
-__device__ __forceinline__ float gl_token(float (&s)[GL_ROWS], const float* __restrict__ a, const float* __restrict__ k,
-                                          const float* __restrict__ q, float vj) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+// One token for a thread's ROWS rows of one column: s <- a s + k v, and sum_r s q per slice of GL_SLICE rows (four partial
+// sums by r mod 4 each).  The sums are formed slice by slice whatever ROWS is, so every kernel form gives the same bits.
+template <int ROWS>
+__device__ __forceinline__ void gl_token(float (&s)[ROWS], const float* __restrict__ a, const float* __restrict__ k,
+                                         const float* __restrict__ q, float vj, float (&out)[ROWS / GL_SLICE]) {
 #pragma unroll
-    for (int r = 0; r < GL_ROWS; r += 4) {
-        const float4 a4 = *reinterpret_cast<const float4*>(a + r);
-        const float4 k4 = *reinterpret_cast<const float4*>(k + r);
-        const float4 q4 = *reinterpret_cast<const float4*>(q + r);
-        s[r + 0] = fmaf(a4.x, s[r + 0], k4.x * vj); acc[0] = fmaf(s[r + 0], q4.x, acc[0]);
-        s[r + 1] = fmaf(a4.y, s[r + 1], k4.y * vj); acc[1] = fmaf(s[r + 1], q4.y, acc[1]);
-        s[r + 2] = fmaf(a4.z, s[r + 2], k4.z * vj); acc[2] = fmaf(s[r + 2], q4.z, acc[2]);
-        s[r + 3] = fmaf(a4.w, s[r + 3], k4.w * vj); acc[3] = fmaf(s[r + 3], q4.w, acc[3]);
+    for (int u = 0; u < ROWS / GL_SLICE; ++u) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = u * GL_SLICE; r < (u + 1) * GL_SLICE; r += 4) {
+            const float4 a4 = *reinterpret_cast<const float4*>(a + r);
+            const float4 k4 = *reinterpret_cast<const float4*>(k + r);
+            const float4 q4 = *reinterpret_cast<const float4*>(q + r);
+            s[r + 0] = fmaf(a4.x, s[r + 0], k4.x * vj); acc[0] = fmaf(s[r + 0], q4.x, acc[0]);
+            s[r + 1] = fmaf(a4.y, s[r + 1], k4.y * vj); acc[1] = fmaf(s[r + 1], q4.y, acc[1]);
+            s[r + 2] = fmaf(a4.z, s[r + 2], k4.z * vj); acc[2] = fmaf(s[r + 2], q4.z, acc[2]);
+            s[r + 3] = fmaf(a4.w, s[r + 3], k4.w * vj); acc[3] = fmaf(s[r + 3], q4.w, acc[3]);
+        }
+        out[u] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
-    return (acc[0] + acc[1]) + (acc[2] + acc[3]);
 }
 
 // The tokens of a stage are copied into shared memory asynchronously while the stage before is computed (two buffers):
 // with one sequence there are few blocks, and a block that waited for its loads between stages spent half its time so.
-template <typename T, int COLS>
+template <typename T, int COLS, int ROWS>
 __global__ void __launch_bounds__(512)
 gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                 const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
@@ -77,18 +82,20 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     extern __shared__ __align__(16) float sh[];
     constexpr int SPW = 32 / COLS;                    // row slices side by side in a warp
     const int slices = (blockDim.x >> 5) * SPW;
-    const int dimP = slices * GL_ROWS;                // dim rounded up to whole slices; the padding rows are zero
+    const int dimP = slices * ROWS;                // dim rounded up to whole slices; the padding rows are zero
     const int buf = GL_TOK * dimP;
     float* qs = sh;                                   // q, k, alpha [2][GL_TOK][dimP] each
     float* ks = qs + 2 * buf;
     float* as = ks + 2 * buf;
     float* vs = as + 2 * buf;                         // v [2][GL_TOK][COLS]
-    float* part = vs + 2 * GL_TOK * COLS;             // the slices' sums [GL_TOK][slices][COLS]
+    constexpr int PER = ROWS / GL_SLICE;              // slices of GL_SLICE rows in a thread's rows
+    const int n_sl = slices * PER;
+    float* part = vs + 2 * GL_TOK * COLS;             // the sums of the slices of GL_SLICE rows [GL_TOK][n_sl][COLS]
     pdl_trigger();
     const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * COLS;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int col = lane % COLS, slice = warp * SPW + lane / COLS;
-    const int j = j0 + col, i0 = slice * GL_ROWS;
+    const int j = j0 + col, i0 = slice * ROWS;
     const int row0 = cu_q[b], row1 = cu_q[b + 1];
     const int slot = seq_slot[b];
     const int width = heads * dim;
@@ -99,9 +106,9 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         qs[tt * dimP + i] = 0.f; ks[tt * dimP + i] = 0.f; as[tt * dimP + i] = 0.f;
     }
     pdl_wait();
-    float s[GL_ROWS];
+    float s[ROWS];
 #pragma unroll
-    for (int r = 0; r < GL_ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
+    for (int r = 0; r < ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
 
     // asynchronous copies of q, k, alpha of the stage that starts at token t0 into buffer p; the caller commits
     auto fetch = [&](int t0, int p) {
@@ -154,25 +161,18 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
         const float* kb = ks + p * buf;
         const float* ab = as + p * buf;
         const float* vb = vs + p * GL_TOK * COLS;
-        // A stage's sums stay in registers until all its tokens are done: with no store between the tokens the loads of
-        // the next tokens start under the arithmetic of this one (the chain per token is the state's FMA alone).
-        float sums[GL_TOK];
-        if (cnt == GL_TOK) {
+#pragma unroll 2
+        for (int tt = 0; tt < cnt; ++tt) {
+            float sums[PER];
+            gl_token<ROWS>(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col], sums);
 #pragma unroll
-            for (int tt = 0; tt < GL_TOK; ++tt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col]);
-        } else {
-#pragma unroll
-            for (int tt = 0; tt < GL_TOK; ++tt)
-                if (tt < cnt) sums[tt] = gl_token(s, ab + tt * dimP + i0, kb + tt * dimP + i0, qb + tt * dimP + i0, vb[tt * COLS + col]);
+            for (int u = 0; u < PER; ++u) part[(tt * n_sl + slice * PER + u) * COLS + col] = sums[u];
         }
-#pragma unroll
-        for (int tt = 0; tt < GL_TOK; ++tt)
-            if (tt < cnt) part[(tt * slices + slice) * COLS + col] = sums[tt];
         __syncthreads();                              // the sums are complete; this stage's buffers are used up
         for (int idx = threadIdx.x; idx < cnt * COLS; idx += blockDim.x) {
             const int tt = idx / COLS, c = idx % COLS;
             float sum = 0.f;
-            for (int w = 0; w < slices; ++w) sum += part[(tt * slices + w) * COLS + c];
+            for (int w = 0; w < n_sl; ++w) sum += part[(tt * n_sl + w) * COLS + c];
             if (j0 + c < vdim) o[(size_t)(t0 + tt) * heads * vdim + h * vdim + j0 + c] = sum;
         }
         if (more) {
@@ -186,35 +186,36 @@ gla_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const 
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     if (j < vdim) {
 #pragma unroll
-        for (int r = 0; r < GL_ROWS; ++r)
+        for (int r = 0; r < ROWS; ++r)
             if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
     }
 }
 
 // One token per sequence (decoding): the same arithmetic without the staging.  grid (sequence, head, ceil(vdim / 32)),
-// a warp per GL_ROWS rows as above; a thread reads its rows' q, k and alpha straight from global memory (16 bytes at a
+// a warp per ROWS rows as above; a thread reads its rows' q, k and alpha straight from global memory (16 bytes at a
 // time where aligned, the same address for all lanes of a warp) and its state elements once, and writes them once.
-template <typename T>
+template <typename T, int ROWS>
 __global__ void __launch_bounds__(512)
 gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ alpha,
                   const T* __restrict__ v, int v_stride, float* __restrict__ state, float* __restrict__ o,
                   const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int heads, int dim, int vdim, int vec) {
-    __shared__ float part[16 * 32];
+    constexpr int PER = ROWS / GL_SLICE;
+    __shared__ float part[32 * 32];                   // up to 256 / GL_SLICE slices
     pdl_trigger();
     const int b = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-    const int j = j0 + lane, i0 = warp * GL_ROWS;
+    const int j = j0 + lane, i0 = warp * ROWS;
     const int t = cu_q[b];
     float* S = state + ((size_t)seq_slot[b] * heads + h) * dim * vdim;
     pdl_wait();
-    float s[GL_ROWS];
+    float s[ROWS];
 #pragma unroll
-    for (int r = 0; r < GL_ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
+    for (int r = 0; r < ROWS; ++r) s[r] = (i0 + r < dim && j < vdim) ? S[(size_t)(i0 + r) * vdim + j] : 0.f;
     const size_t g = (size_t)t * heads * dim + (size_t)h * dim + i0;
-    float a[GL_ROWS], kk[GL_ROWS], qq[GL_ROWS];
-    if (vec && i0 + GL_ROWS <= dim) {
+    float a[ROWS], kk[ROWS], qq[ROWS];
+    if (vec && i0 + ROWS <= dim) {
 #pragma unroll
-        for (int r = 0; r < GL_ROWS; r += 4) {
+        for (int r = 0; r < ROWS; r += 4) {
             const float4 a4 = *reinterpret_cast<const float4*>(alpha + g + r);
             const float4 k4 = *reinterpret_cast<const float4*>(k + g + r);
             const float4 q4 = *reinterpret_cast<const float4*>(q + g + r);
@@ -224,52 +225,78 @@ gla_decode_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         }
     } else {
 #pragma unroll
-        for (int r = 0; r < GL_ROWS; ++r) {
+        for (int r = 0; r < ROWS; ++r) {
             const bool in = i0 + r < dim;
             a[r] = in ? alpha[g + r] : 0.f; kk[r] = in ? k[g + r] : 0.f; qq[r] = in ? q[g + r] : 0.f;
         }
     }
     const float vj = j < vdim ? Cvt<T>::to_f32(v[(size_t)t * v_stride + h * vdim + j]) : 0.f;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < GL_ROWS; ++r) {               // the same operations in the same order as gl_token
-        s[r] = fmaf(a[r], s[r], kk[r] * vj);
-        acc[r & 3] = fmaf(s[r], qq[r], acc[r & 3]);
+    for (int u = 0; u < PER; ++u) {                   // the same operations in the same order as gl_token
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = u * GL_SLICE; r < (u + 1) * GL_SLICE; ++r) {
+            s[r] = fmaf(a[r], s[r], kk[r] * vj);
+            acc[r & 3] = fmaf(s[r], qq[r], acc[r & 3]);
+        }
+        part[(warp * PER + u) * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
-    part[warp * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     if (j < vdim) {
 #pragma unroll
-        for (int r = 0; r < GL_ROWS; ++r)
+        for (int r = 0; r < ROWS; ++r)
             if (i0 + r < dim) S[(size_t)(i0 + r) * vdim + j] = s[r];
     }
     __syncthreads();
     if (warp == 0 && j < vdim) {
         float sum = 0.f;
-        for (int w = 0; w < warps; ++w) sum += part[w * 32 + lane];
+        for (int w = 0; w < warps * PER; ++w) sum += part[w * 32 + lane];
         o[(size_t)t * heads * vdim + h * vdim + j] = sum;
     }
 }
 
-template <typename T, int COLS>
+template <typename T, int COLS, int ROWS>
 static int launch_scan_cols(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
                             float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int vec,
                             cudaStream_t st) {
     constexpr int SPW = 32 / COLS;
-    const int slices = ((dim + GL_ROWS - 1) / GL_ROWS + SPW - 1) / SPW * SPW;
+    const int slices = ((dim + ROWS - 1) / ROWS + SPW - 1) / SPW * SPW;
     const int warps = slices / SPW;
     const int gz = (vdim + COLS - 1) / COLS;
     if (gz > 65535) return RF_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(6 * GL_TOK * slices * GL_ROWS + 2 * GL_TOK * COLS + GL_TOK * slices * COLS) * sizeof(float);
+    const size_t smem = (size_t)(6 * GL_TOK * slices * ROWS + 2 * GL_TOK * COLS + GL_TOK * slices * (ROWS / GL_SLICE) * COLS) * sizeof(float);
     static size_t configured = 48 * 1024;
     if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, COLS, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = smem;
     }
-    rf_launch(gla_scan_kernel<T, COLS>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
+    rf_launch(gla_scan_kernel<T, COLS, ROWS>, dim3(B, heads, gz), dim3(warps * 32), smem, st, q, k, alpha, reinterpret_cast<const T*>(v),
               v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
     RF_LAUNCH_CHECK();
     return 0;
+}
+
+// ROWS: the rows of the state in a thread's registers (see launch_scan).
+template <typename T, int ROWS>
+static int launch_scan_rows(const float* q, const float* k, const float* alpha, const void* v, int v_stride, float* state,
+                            float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
+                            int sms, cudaStream_t st) {
+    const int warps = (dim + ROWS - 1) / ROWS;
+    const int gz = (vdim + 31) / 32;
+    if (warps > 16 || gz > 65535) return RF_ERR_UNSUPPORTED;
+    // rows of q, k, alpha are copied 16 bytes at a time where a head's slice of every token starts on such a boundary
+    const int vec = dim % 4 == 0 && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                                       reinterpret_cast<uintptr_t>(alpha)) & 15);
+    if (one_token) {
+        rf_launch(gla_decode_kernel<T, ROWS>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
+                  v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
+    if (sms <= 0) sms = 148;
+    if ((long long)B * heads * gz < sms)              // few blocks: narrower ones, twice as many
+        return launch_scan_cols<T, 16, ROWS>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
+    return launch_scan_cols<T, 32, ROWS>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
 }
 
 template <typename T>
@@ -277,22 +304,16 @@ static int launch_scan(const float* q, const float* k, const float* alpha, const
                        float* o, const int* cu_q, const int* seq_slot, int B, int heads, int dim, int vdim, int one_token,
                        int sms, cudaStream_t st) {
     if (B <= 0) return 0;
-    const int warps = (dim + GL_ROWS - 1) / GL_ROWS;
-    const int gz = (vdim + 31) / 32;
-    if (dim <= 0 || warps > 16 || vdim <= 0 || heads <= 0 || heads > 65535 || gz > 65535) return RF_ERR_UNSUPPORTED;
-    // rows of q, k, alpha are copied 16 bytes at a time where a head's slice of every token starts on such a boundary
-    const int vec = dim % 4 == 0 && !((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
-                                       reinterpret_cast<uintptr_t>(alpha)) & 15);
-    if (one_token) {
-        rf_launch(gla_decode_kernel<T>, dim3(B, heads, gz), dim3(warps * 32), 0, st, q, k, alpha, reinterpret_cast<const T*>(v),
-                  v_stride, state, o, cu_q, seq_slot, heads, dim, vdim, vec);
-        RF_LAUNCH_CHECK();
-        return 0;
-    }
+    if (dim <= 0 || dim > 256 || vdim <= 0 || heads <= 0 || heads > 65535) return RF_ERR_UNSUPPORTED;
+    // Eight rows a thread (twice the warps, half the chain of each) while the step has too few (sequence, head) pairs to
+    // fill the SMs twice over, sixteen beyond (fewer instructions per product) and for more than 128 key channels (a block
+    // has at most sixteen warps).  Measured on 16 heads of 128 x 128, 2,048 tokens a sequence: one sequence 533 us with
+    // sixteen rows, 434 us with eight; eight sequences 1,700 against 2,518 us.  The sums are formed per slice of GL_SLICE
+    // rows in both, so the choice changes no bit.
     if (sms <= 0) sms = 148;
-    if ((long long)B * heads * gz < sms)              // few blocks: narrower ones, twice as many
-        return launch_scan_cols<T, 16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
-    return launch_scan_cols<T, 32>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, vec, st);
+    if (dim <= 128 && (long long)B * heads * ((vdim + 31) / 32) < 2LL * sms)
+        return launch_scan_rows<T, 8>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
+    return launch_scan_rows<T, 16>(q, k, alpha, v, v_stride, state, o, cu_q, seq_slot, B, heads, dim, vdim, one_token, sms, st);
 }
 
 template <typename T>
