@@ -3,6 +3,8 @@ from __future__ import annotations
 
 from typing import Dict
 
+import torch
+
 from .base import BLOCKS, Block, FeedForward, Mixer, Norm, Part
 
 
@@ -61,7 +63,6 @@ class ReadsStream(Norm):
         if prepared is not None and prepared[0] is self and stream.pending is None:
             return prepared[1]
         stream.flush()
-        import torch
         return stream.h if ctx.compute_dtype == torch.float32 else kernels.round_rows(stream.h, ctx.compute_dtype)
 
     def cuda_modules(self, compute_dtype):
@@ -135,7 +136,6 @@ class SandwichBlock(Block):
             nxt = None
         stream.flush()
         stream.prepared = None
-        import torch
         y = kernels.branch_norm_add(stream.h, branches, weight, eps, ctx.compute_dtype, extra=extra,
                                     next_weight=nxt[0] if nxt is not None else None,
                                     next_rounded=next_norm is READS_STREAM and ctx.compute_dtype != torch.float32)

@@ -5,7 +5,6 @@ functions, with inputs made so that a key one place off, a lost state or a missi
 import json
 import os
 import subprocess
-import sys
 
 import numpy as np
 import pytest
